@@ -1,0 +1,30 @@
+// Byte layout of the packed (LayerNorm-folded) weight buffers.
+#pragma once
+#include <stddef.h>
+
+namespace b200ta {
+
+constexpr int kC = 128;         // pair channels
+constexpr int kHeads = 4;
+constexpr int kHeadDim = 32;
+constexpr int kHidden = 512;    // transition hidden width
+
+// ---- triangle-attention node -------------------------------------------------
+// Rows of the folded in-projection: q(128) k(128) v(128) g(128) bias(4) pad(12).
+constexpr int kNodeRows = 528;
+constexpr size_t kNodeWOff = 0;                                   // bf16 [528][128]
+constexpr size_t kNodeScOff = kNodeWOff + size_t(kNodeRows) * kC * 2;  // float2 [528] {rowsum, const}
+constexpr size_t kNodeWoOff = kNodeScOff + size_t(kNodeRows) * 8;      // bf16 [128][128] (o_proj)
+constexpr size_t kNodeBoOff = kNodeWoOff + size_t(kC) * kC * 2;        // float [128]
+constexpr size_t kNodePackBytes = ((kNodeBoOff + kC * 4 + 255) / 256) * 256;
+
+// ---- transition ---------------------------------------------------------------
+// Rows of the folded first linear: value(512) then gate(512, pre-halved for the
+// tanh form of silu).
+constexpr int kTransRows = 2 * kHidden;
+constexpr size_t kTransW1Off = 0;                                         // bf16 [1024][128]
+constexpr size_t kTransScOff = kTransW1Off + size_t(kTransRows) * kC * 2; // float2 [1024]
+constexpr size_t kTransW2Off = kTransScOff + size_t(kTransRows) * 8;      // bf16 [128][512]
+constexpr size_t kTransPackBytes = ((kTransW2Off + size_t(kC) * kHidden * 2 + 255) / 256) * 256;
+
+}  // namespace b200ta

@@ -1,0 +1,125 @@
+// Weight packing: folds LayerNorm's affine into the linear layer that follows it.
+//
+// For a row w of a projection applied to LN(z) = (z - mu) * rstd * gamma + beta:
+//   proj = rstd * sum_c (z_c - mu) * (gamma_c * w_c)  +  sum_c beta_c * w_c  + b
+// Subtracting the mean of (gamma*w) from the row leaves the first sum unchanged
+// (sum_c (z_c - mu) = 0), and keeps the tensor-core dot product of raw z rows with
+// the folded row free of a large common-mode term.  The bf16 rounding of the
+// centred row makes its sum slightly non-zero; that sum is stored so the GEMM
+// epilogue can subtract mu * rowsum exactly:
+//   proj = rstd * (acc - mu * rowsum) + const.
+#include "common.cuh"
+#include "layout.h"
+
+namespace b200ta {
+namespace {
+
+__device__ __forceinline__ float load_w(const void* p, int dtype, size_t i) {
+  return dtype == B200TA_DTYPE_F32 ? reinterpret_cast<const float*>(p)[i]
+                                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// One block of 128 threads per output row.  Rows [0, rows_a) come from `wa`, rows
+// [rows_a, rows_a + rows_b) from `wb`, the rest are zero.  Rows in
+// [scale_from, scale_to) are multiplied by `scale` (constant term included).
+__global__ void fold_rows_kernel(const void* wa, int rows_a, const void* wb, int rows_b,
+                                 const void* bias_a, const void* gamma, const void* beta, int dtype,
+                                 int scale_from, int scale_to, float scale, __nv_bfloat16* wp,
+                                 float2* sc) {
+  const int n = blockIdx.x;
+  const int c = threadIdx.x;
+  __shared__ float red[3][4];
+  float w = 0.f, b = 0.f;
+  if (n < rows_a) {
+    w = load_w(wa, dtype, size_t(n) * kC + c);
+    if (bias_a != nullptr) b = load_w(bias_a, dtype, n);
+  } else if (n < rows_a + rows_b) {
+    w = load_w(wb, dtype, size_t(n - rows_a) * kC + c);
+  }
+  const float s = (n >= scale_from && n < scale_to) ? scale : 1.f;
+  w *= s;
+  b *= s;
+  const float g = load_w(gamma, dtype, c);
+  const float be = load_w(beta, dtype, c);
+  float wg = w * g;
+  float cterm = w * be;
+  // block reductions over the 128 channels
+  auto block_sum = [&](float v, int slot) -> float {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) red[slot][threadIdx.x >> 5] = v;
+    __syncthreads();
+    return red[slot][0] + red[slot][1] + red[slot][2] + red[slot][3];
+  };
+  const float mean = block_sum(wg, 0) * (1.f / kC);
+  const float csum = block_sum(cterm, 1);
+  const __nv_bfloat16 q = __float2bfloat16_rn(wg - mean);
+  wp[size_t(n) * kC + c] = q;
+  const float rowsum = block_sum(__bfloat162float(q), 2);
+  if (c == 0) sc[n] = make_float2(rowsum, csum + b);
+}
+
+__global__ void convert_kernel(const void* src, int dtype, size_t n, __nv_bfloat16* dst_bf16,
+                               float* dst_f32) {
+  size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = src == nullptr ? 0.f : load_w(src, dtype, i);
+  if (dst_bf16 != nullptr) dst_bf16[i] = __float2bfloat16_rn(v);
+  if (dst_f32 != nullptr) dst_f32[i] = v;
+}
+
+int check_dtype(int dtype) {
+  if (dtype != B200TA_DTYPE_BF16 && dtype != B200TA_DTYPE_F32)
+    return fail(B200TA_ERR_INVALID, "weight_dtype must be B200TA_DTYPE_BF16 or B200TA_DTYPE_F32");
+  return B200TA_OK;
+}
+
+}  // namespace
+}  // namespace b200ta
+
+extern "C" {
+
+size_t b200ta_node_pack_bytes(void) { return b200ta::kNodePackBytes; }
+size_t b200ta_transition_pack_bytes(void) { return b200ta::kTransPackBytes; }
+
+int b200ta_pack_node_weights(const void* ln_w, const void* ln_b, const void* w_in, const void* b_in,
+                             const void* w_bias, const void* w_out, const void* b_out,
+                             int weight_dtype, void* packed, void* stream) {
+  using namespace b200ta;
+  B200TA_REQUIRE(ln_w && ln_b && w_in && w_bias && w_out && packed, "pack_node_weights: NULL pointer");
+  B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "pack_node_weights: packed must be 256-byte aligned");
+  int rc = check_dtype(weight_dtype);
+  if (rc != B200TA_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* base = static_cast<char*>(packed);
+  constexpr float kLog2e = 1.4426950408889634f;
+  fold_rows_kernel<<<kNodeRows, kC, 0, s>>>(
+      w_in, 4 * kHeads * kHeadDim, w_bias, kHeads, b_in, ln_w, ln_b, weight_dtype, 4 * kHeads * kHeadDim,
+      4 * kHeads * kHeadDim + kHeads, kLog2e, reinterpret_cast<__nv_bfloat16*>(base + kNodeWOff),
+      reinterpret_cast<float2*>(base + kNodeScOff));
+  convert_kernel<<<(kC * kC + 255) / 256, 256, 0, s>>>(w_out, weight_dtype, size_t(kC) * kC,
+                                                       reinterpret_cast<__nv_bfloat16*>(base + kNodeWoOff), nullptr);
+  convert_kernel<<<1, kC, 0, s>>>(b_out, weight_dtype, kC, nullptr, reinterpret_cast<float*>(base + kNodeBoOff));
+  B200TA_CHECK_CUDA(cudaGetLastError());
+  return B200TA_OK;
+}
+
+int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const void* w1, const void* w2,
+                                   int weight_dtype, void* packed, void* stream) {
+  using namespace b200ta;
+  B200TA_REQUIRE(ln_w && ln_b && w1 && w2 && packed, "pack_transition_weights: NULL pointer");
+  B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "pack_transition_weights: packed must be 256-byte aligned");
+  int rc = check_dtype(weight_dtype);
+  if (rc != B200TA_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* base = static_cast<char*>(packed);
+  // gate rows are halved: silu(g) = h + h * tanh(h) with h = g / 2
+  fold_rows_kernel<<<kTransRows, kC, 0, s>>>(w1, kTransRows, nullptr, 0, nullptr, ln_w, ln_b, weight_dtype, kHidden,
+                                             kTransRows, 0.5f, reinterpret_cast<__nv_bfloat16*>(base + kTransW1Off),
+                                             reinterpret_cast<float2*>(base + kTransScOff));
+  convert_kernel<<<(kC * kHidden + 255) / 256, 256, 0, s>>>(w2, weight_dtype, size_t(kC) * kHidden,
+                                                            reinterpret_cast<__nv_bfloat16*>(base + kTransW2Off), nullptr);
+  B200TA_CHECK_CUDA(cudaGetLastError());
+  return B200TA_OK;
+}
+
+}  // extern "C"

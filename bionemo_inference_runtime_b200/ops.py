@@ -1,0 +1,201 @@
+"""Tensor-level wrappers over the C ABI (``include/b200ta.h``).
+
+PyTorch is used here only for device memory and the current stream; every
+computation is a call into libb200ta.so.  Shapes follow the reference layers:
+``z`` is a pair tensor ``[B, I, J, 128]``; the ending node runs the same kernels
+on the transposed view by swapping the two pair strides (no copy).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+C = 128
+HEADS = 4
+HEAD_DIM = 32
+HIDDEN = 512
+LOG2E = 1.4426950408889634
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _require_cuda_bf16(name: str, t: torch.Tensor) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this package has no CPU path)")
+    if t.dtype != torch.bfloat16:
+        raise ValueError(f"{name} must be bfloat16, got {t.dtype}")
+
+
+def _weight_dtype(*tensors: torch.Tensor | None) -> int:
+    dtypes = {t.dtype for t in tensors if t is not None}
+    if dtypes == {torch.bfloat16}:
+        return _lib.DTYPE_BF16
+    if dtypes == {torch.float32}:
+        return _lib.DTYPE_F32
+    raise ValueError(f"weights must all be bfloat16 or all float32, got {sorted(map(str, dtypes))}")
+
+
+def _contig(t: torch.Tensor | None) -> torch.Tensor | None:
+    return None if t is None else t.contiguous()
+
+
+def pack_node_weights(ln_w, ln_b, w_in, b_in, w_bias, w_out, b_out) -> torch.Tensor:
+    """Fold LayerNorm into the q/k/v/g + triangle-bias projection; returns the opaque packed buffer."""
+    ts = [_contig(t) for t in (ln_w, ln_b, w_in, b_in, w_bias, w_out, b_out)]
+    if tuple(ts[2].shape) != (4 * HEADS * HEAD_DIM, C) or tuple(ts[4].shape) != (HEADS, C) or tuple(ts[5].shape) != (C, HEADS * HEAD_DIM):
+        raise ValueError(
+            f"kernels are specialised for c_z={C}, {HEADS} heads of {HEAD_DIM}: got in_proj {tuple(ts[2].shape)}, "
+            f"pair_bias_proj {tuple(ts[4].shape)}, o_proj {tuple(ts[5].shape)}"
+        )
+    dt = _weight_dtype(*ts)
+    packed = torch.empty(_lib.load().b200ta_node_pack_bytes(), dtype=torch.uint8, device=ts[0].device)
+    _lib.call("b200ta_pack_node_weights", *[_ptr(t) for t in ts], dt, packed.data_ptr(), _stream())
+    return packed
+
+
+def pack_transition_weights(ln_w, ln_b, w1, w2) -> torch.Tensor:
+    """Fold LayerNorm into fused_fc2_fc1 (gate rows pre-halved); returns the opaque packed buffer."""
+    ts = [_contig(t) for t in (ln_w, ln_b, w1, w2)]
+    if tuple(ts[2].shape) != (2 * HIDDEN, C) or tuple(ts[3].shape) != (C, HIDDEN):
+        raise ValueError(f"kernel is specialised for dim={C}, hidden={HIDDEN}: got {tuple(ts[2].shape)}, {tuple(ts[3].shape)}")
+    dt = _weight_dtype(*ts)
+    packed = torch.empty(_lib.load().b200ta_transition_pack_bytes(), dtype=torch.uint8, device=ts[0].device)
+    _lib.call("b200ta_pack_transition_weights", *[_ptr(t) for t in ts], dt, packed.data_ptr(), _stream())
+    return packed
+
+
+def _pair_strides(z: torch.Tensor, ending: bool) -> tuple[int, int, int, int, int, int]:
+    """(B, R, S, stride_b, stride_r, stride_s) of a [B, I, J, C] tensor as the kernels see it."""
+    if z.dim() != 4 or z.shape[-1] != C or z.stride(-1) != 1:
+        raise ValueError(f"expected a [B, I, J, {C}] tensor with unit channel stride, got {tuple(z.shape)}")
+    B, I, J, _ = z.shape
+    sb, si, sj, _ = z.stride()
+    return (B, J, I, sb, sj, si) if ending else (B, I, J, sb, si, sj)
+
+
+def pad8(n: int) -> int:
+    return -(-n // 8) * 8
+
+
+def prologue(z, packed, eps: float = 1e-5, *, ending: bool = False, want_qkvg: bool = True,
+             qkvg: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+             want_bias: bool = True, transposed_bias: bool = False):
+    """LayerNorm + q/k/v/g projection + triangle-bias projection.
+
+    Returns ``(qkvg, bias)``: ``qkvg`` is ``[4, B*R, H, S, D]`` (q, k, v, g planes, head-major),
+    ``bias`` is ``[B, H, S_q, S_pad]`` scaled by log2(e).  With ``ending`` the rows R run over
+    the second pair axis of ``z``.
+    """
+    _require_cuda_bf16("z", z)
+    B, R, S, sb, sr, ss = _pair_strides(z, ending)
+    S_pad = pad8(S)
+    if want_qkvg and qkvg is None:
+        qkvg = torch.empty((4, B * R, HEADS, S, HEAD_DIM), dtype=torch.bfloat16, device=z.device)
+    if want_bias and bias is None:
+        if R != S:
+            raise ValueError("the triangle bias needs a square pair tensor")
+        bias = torch.empty((B, HEADS, R, S_pad), dtype=torch.bfloat16, device=z.device)
+    if qkvg is not None:
+        qs = (qkvg.stride(0), qkvg.stride(1), qkvg.stride(2), qkvg.stride(3))
+    else:
+        qs = (0, 0, 0, 0)
+    if bias is not None:
+        bs = (bias.stride(0), bias.stride(1), bias.stride(2), bias.stride(3))
+        if transposed_bias:
+            bs = (bs[0], bs[1], bs[3], bs[2])
+    else:
+        bs = (0, 0, 0, 0)
+    _lib.call("b200ta_prologue", z.data_ptr(), sb, sr, ss, packed.data_ptr(), float(eps), _ptr(qkvg), *qs,
+              1 if want_qkvg else 0, _ptr(bias if want_bias else None), *bs, B, R, S, S_pad, _stream())
+    return qkvg, bias
+
+
+def attention(qkvg: torch.Tensor, bias: torch.Tensor, lengths: torch.Tensor | None, B: int, R: int, S: int, *,
+              gate: bool = True, out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
+              empty_row_mode: int = _lib.EMPTY_ROW_UNIFORM, scale: float | None = None) -> torch.Tensor:
+    """Biased, length-masked attention over the head-major ``qkvg`` planes; returns ``[B, R, S, 128]``."""
+    _require_cuda_bf16("qkvg", qkvg)
+    _require_cuda_bf16("bias", bias)
+    if out is None:
+        out = torch.empty((B, R, S, C), dtype=torch.bfloat16, device=qkvg.device)
+    if scale is None:
+        scale = 1.0 / math.sqrt(HEAD_DIM)
+    if lengths is not None:
+        if lengths.dtype != torch.int32 or not lengths.is_cuda:
+            raise ValueError("lengths must be a CUDA int32 tensor")
+        if lengths.numel() == B * R:
+            lengths = lengths.reshape(B, R)
+            ls = (lengths.stride(0), lengths.stride(1))
+        elif lengths.numel() == B:
+            lengths = lengths.reshape(B)
+            ls = (lengths.stride(0), 0)
+        else:
+            raise ValueError(f"lengths must hold B*R={B * R} or B={B} values, got {lengths.numel()}")
+    else:
+        ls = (0, 0)
+    q, k, v, g = qkvg[0], qkvg[1], qkvg[2], qkvg[3]
+    for t in (k, v, g):
+        if t.stride() != q.stride():
+            raise ValueError("q, k, v, g planes must share strides")
+    o4 = out.view(B * R, S, HEADS, HEAD_DIM)
+    _lib.call("b200ta_attention", q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr() if gate else None,
+              q.stride(0), q.stride(1), q.stride(2), bias.data_ptr(), bias.stride(0), bias.stride(1), bias.stride(2),
+              _ptr(lengths), *ls, o4.data_ptr(), o4.stride(0), o4.stride(1), o4.stride(2), _ptr(lse), float(scale),
+              int(empty_row_mode), B, R, S, bias.shape[-1], _stream())
+    return out
+
+
+def epilogue(og: torch.Tensor, packed: torch.Tensor, residual: torch.Tensor | None, out: torch.Tensor | None = None,
+             *, ending: bool = False) -> torch.Tensor:
+    """``out = residual + og · W_oᵀ + b_o``.
+
+    ``og`` is ``[B, R, S, 128]`` in kernel order; ``residual`` / ``out`` are pair tensors ``[B, I, J, 128]`` in the
+    caller's order (for ``ending`` they are addressed through swapped strides).
+    """
+    _require_cuda_bf16("og", og)
+    B, R, S, _ = og.shape
+    if out is None:
+        out = torch.empty((B, S, R, C) if ending else (B, R, S, C), dtype=torch.bfloat16, device=og.device)
+    oB, oR, oS, osb, osr, oss = _pair_strides(out, ending)
+    if (oB, oR, oS) != (B, R, S):
+        raise ValueError(f"out shape {tuple(out.shape)} does not match og {tuple(og.shape)}")
+    if residual is not None:
+        _require_cuda_bf16("residual", residual)
+        rB, rR, rS, rsb, rsr, rss = _pair_strides(residual, ending)
+        if (rB, rR, rS) != (B, R, S):
+            raise ValueError(f"residual shape {tuple(residual.shape)} does not match og {tuple(og.shape)}")
+    else:
+        rsb = rsr = rss = 0
+    _lib.call("b200ta_epilogue", og.data_ptr(), og.stride(0), og.stride(1), og.stride(2), packed.data_ptr(),
+              _ptr(residual), rsb, rsr, rss, out.data_ptr(), osb, osr, oss, B, R, S, _stream())
+    return out
+
+
+def transition(x: torch.Tensor, packed: torch.Tensor, mask: torch.Tensor | None = None, eps: float = 1e-5, *,
+               residual: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused LayerNorm -> SwiGLU MLP (-> mask) (-> + x) over the rows of ``x[..., 128]``."""
+    _require_cuda_bf16("x", x)
+    if x.shape[-1] != C:
+        raise ValueError(f"last dimension must be {C}")
+    x2 = x.reshape(-1, C) if x.is_contiguous() else None
+    if x2 is None:
+        raise ValueError("transition needs a contiguous input")
+    if out is None:
+        out = torch.empty_like(x)
+    elif not out.is_contiguous() or out.shape != x.shape:
+        raise ValueError("out must be contiguous and shaped like x")
+    if mask is not None:
+        mask = mask.to(torch.bfloat16).expand(x.shape[:-1]).contiguous()
+    _lib.call("b200ta_transition", x2.data_ptr(), C, _ptr(mask), packed.data_ptr(), float(eps), out.data_ptr(), C,
+              x2.shape[0], 1 if residual else 0, _stream())
+    return out

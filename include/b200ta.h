@@ -1,0 +1,176 @@
+/*
+ * b200ta — C ABI of the sm_100a triangle-attention / pair-transition kernels.
+ *
+ * Every entry point takes plain device pointers, sizes, element strides and a
+ * CUDA stream (passed as void*; NULL = the legacy default stream).  Calls only
+ * enqueue work on that stream: they never synchronise, never allocate device
+ * memory (the caller passes workspaces) and return 0 or a negative status code.
+ * b200ta_last_error() gives the reason for the calling thread's last failure.
+ *
+ * Tensors are bf16 unless stated; "positions" are the B*R*S cells of a pair
+ * tensor z[B, R, S, 128] addressed through element strides, so the ending node
+ * (which works on the transposed pair tensor) passes the same buffers with the
+ * R and S strides swapped instead of materialising a transpose.
+ *
+ * The first call on a device creates a small per-device state (a mapped status
+ * word); make it outside any stream capture.
+ *
+ * Each declaration cites the interface of the reference runtime it replaces
+ * (paths are relative to the reference project root).
+ */
+#ifndef B200TA_H_
+#define B200TA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200TA_OK 0
+#define B200TA_ERR_INVALID (-1)     /* bad argument: shape, alignment, stride, null pointer */
+#define B200TA_ERR_CUDA (-2)        /* a CUDA runtime call failed */
+#define B200TA_ERR_DRIVER (-3)      /* tensor-map encoding failed / driver entry point missing */
+#define B200TA_ERR_DEVICE_WAIT (-4) /* a kernel gave up on a bounded wait (status word) */
+#define B200TA_ERR_UNSUPPORTED (-5) /* valid request outside what the kernels cover */
+
+/* Fixed model dimensions the kernels are specialised for (Boltz-2 / AF3 pair track). */
+#define B200TA_C 128       /* pair channels c_z */
+#define B200TA_HEADS 4     /* attention heads */
+#define B200TA_HEAD_DIM 32 /* head width */
+#define B200TA_HIDDEN 512  /* transition hidden width (4 x c_z) */
+
+#define B200TA_DTYPE_BF16 0
+#define B200TA_DTYPE_F32 1
+
+#define B200TA_EMPTY_ROW_ZEROS 0   /* rows with no valid key produce 0 (fused reference kernels) */
+#define B200TA_EMPTY_ROW_UNIFORM 1 /* rows with no valid key average V over all keys (eager reference) */
+
+/* Library ABI version (major*100 + minor). */
+int b200ta_version(void);
+
+/* Message describing the calling thread's most recent non-zero return. */
+const char* b200ta_last_error(void);
+
+/*
+ * Reads (*status) the current device's status word: 0, or B200TA_ERR_DEVICE_WAIT
+ * if any kernel since the last reset abandoned a bounded wait.  Synchronise the
+ * stream first if the answer must cover work still in flight.
+ * Replaces: error propagation of cubin launches, cpp/kernels/cubin_runtime.h
+ * (the reference has no device-side status; its kernels have unbounded waits).
+ */
+int b200ta_device_status(int* status);
+int b200ta_reset_device_status(void);
+
+/* ---- weight packing --------------------------------------------------------
+ *
+ * Folds LayerNorm(gamma, beta) into the projection that follows it, so the
+ * kernels can feed raw bf16 rows of z to the tensor cores and apply mean / rstd
+ * in the GEMM epilogue.  Packed buffers are opaque, device-resident and must be
+ * rebuilt when any source weight changes.
+ * Replaces: pack_weights, bionemo_ir/_torch/custom_ops/transition_mlp_w_norm/ops.py:198-302
+ * (same idea, applied here to the attention in-projection as well).
+ */
+
+/* Bytes of a packed node / transition weight buffer (256-byte aligned pointer required). */
+size_t b200ta_node_pack_bytes(void);
+size_t b200ta_transition_pack_bytes(void);
+
+/*
+ * ln_w, ln_b: [128].  w_in: [512,128], rows ordered q,k,v,g (head-major inside
+ * each, as Linear.load_weights builds it, bionemo_ir/_torch/layers/linear.py:184-198).
+ * b_in: [512] or NULL.  w_bias: [4,128] (pair_bias_proj).  w_out: [128,128]
+ * (o_proj), b_out: [128] or NULL.  weight_dtype: B200TA_DTYPE_* of all six.
+ */
+int b200ta_pack_node_weights(const void* ln_w, const void* ln_b, const void* w_in,
+                             const void* b_in, const void* w_bias, const void* w_out,
+                             const void* b_out, int weight_dtype, void* packed, void* stream);
+
+/*
+ * ln_w, ln_b: [128].  w1: [1024,128] (fused_fc2_fc1: value rows first, gate rows
+ * second).  w2: [128,512] (fc3).
+ */
+int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const void* w1,
+                                   const void* w2, int weight_dtype, void* packed, void* stream);
+
+/* ---- triangle-attention node ------------------------------------------------- */
+
+/*
+ * Prologue: LayerNorm over channels, the q/k/v/gate projection and the 4-head
+ * triangle-bias projection of every position, one tcgen05 GEMM per 128-position tile.
+ *
+ *   z          [B,R,S,128] via element strides (zs_b, zs_r, zs_s); channel stride 1.
+ *   qkvg       output, four planes (q,k,v,g) of [B*R, 4 heads, S, 32]:
+ *              element (which, br, h, s, d) at which*qs_which + br*qs_br + h*qs_h + s*qs_s + d.
+ *   bias       output, bias[b,h,q=r,k=s] * log2(e) at b*bs_b + h*bs_h + r*bs_q + s*bs_k;
+ *              entries S <= s < S_pad are written as zero.  May be NULL (no bias written).
+ *   want_qkvg  0 = bias only (used to finish the bias of all rows before a
+ *              row-chunked pass), 1 = both.
+ *
+ * Replaces: LNPairBias (bionemo_ir/dsl_kernels/triton/ln_pair_bias.py:261-322) plus the
+ * in_proj GEMM (bionemo_ir/_torch/layers/attention.py:257-258).
+ */
+int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, const void* packed,
+                    float eps, void* qkvg, int64_t qs_which, int64_t qs_br, int64_t qs_h,
+                    int64_t qs_s, int want_qkvg, void* bias, int64_t bs_b, int64_t bs_h,
+                    int64_t bs_q, int64_t bs_k, int B, int R, int S, int S_pad, void* stream);
+
+/*
+ * Attention core.  For every (b, r, h) and query s:
+ *   o[s,:] = softmax_t( scale * q[s]·k[t] + bias[b,h,s,t] ; t < len[b,r] ) · v[t,:]
+ * optionally multiplied by sigmoid(gate) in the epilogue.
+ *
+ *   q,k,v,gate [B*R, 4, S, 32] via element strides (br, h, s); d stride 1; gate may be NULL.
+ *   bias       [B, 4, S, S_pad] with log2(e) already folded in (as b200ta_prologue
+ *              writes it) when bias_is_log2 != 0, plain otherwise... (bias_is_log2 must be 1
+ *              in this version); element strides (b, h, q); key stride 1; S_pad % 8 == 0.
+ *   lengths    int32, len[b,r] at b*ls_b + r*ls_r (ls_r = 0 broadcasts one length per item).
+ *              NULL = every key valid.
+ *   out        [B*R, S, 4, 32] via element strides (br, s, h); d stride 1.
+ *   lse        optional fp32 natural-log-sum-exp, [B*R, S, 4] contiguous, or NULL.
+ *   empty_row_mode  B200TA_EMPTY_ROW_*.
+ *
+ * Replaces: triangle_attention.launch(config, LaunchParams)
+ * (cpp/kernels/cutedsl_triangle_attention/launcher.h:515-532, launcher.cpp:548-627) and the
+ * sigmoid gate of bionemo_ir/_torch/layers/attention.py:285-287.
+ */
+int b200ta_attention(const void* q, const void* k, const void* v, const void* gate, int64_t s_br,
+                     int64_t s_h, int64_t s_s, const void* bias, int64_t bs_b, int64_t bs_h,
+                     int64_t bs_q, const int32_t* lengths, int64_t ls_b, int64_t ls_r, void* out,
+                     int64_t os_br, int64_t os_s, int64_t os_h, float* lse, float softmax_scale,
+                     int empty_row_mode, int B, int R, int S, int S_pad, void* stream);
+
+/*
+ * Epilogue: out = residual + og · W_oᵀ + b_o, with og = o ⊙ sigmoid(g) as written by
+ * b200ta_attention.
+ *
+ *   og        [B,R,S,128] via element strides (b, r, s).
+ *   residual  [B,R,S,128] via element strides, or NULL (out = update only).
+ *   out       [B,R,S,128] via element strides; may alias residual.
+ *
+ * Replaces: AttnEpilogue.__call__ (bionemo_ir/_torch/custom_ops/attn_epilogue/ops.py:195-254).
+ */
+int b200ta_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, const void* packed,
+                    const void* residual, int64_t rs_b, int64_t rs_r, int64_t rs_s, void* out,
+                    int64_t os_b, int64_t os_r, int64_t os_s, int B, int R, int S, void* stream);
+
+/* ---- pair transition ---------------------------------------------------------------
+ *
+ * out = [x +] mask * ( (silu(gate) * value) · W2ᵀ ),  [value|gate] = LayerNorm(x) · W1ᵀ,
+ * one kernel, hidden activation kept on chip.
+ *
+ *   x     [rows,128] bf16, row stride xs (elements).   out likewise (may alias x).
+ *   mask  one bf16 value per row (contiguous) or NULL.
+ *   add_residual  1: out = x + ..., 0: out = update.
+ *
+ * Replaces: transition_mlp_w_norm launch
+ * (bionemo_ir/_torch/custom_ops/transition_mlp_w_norm/ops.py:349-518).
+ */
+int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* packed, float eps,
+                      void* out, int64_t os, int64_t rows, int add_residual, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200TA_H_ */

@@ -1,0 +1,208 @@
+"""CPU oracle for the triangle-attention node and the pair transition.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the product package may import this
+module: it exists so the tests, the smoke check and the CPU-baseline leg of the
+benchmark can compare the CUDA path against a slow, plain restatement of the
+reference algorithm.  It runs on the CPU with ordinary PyTorch tensor ops (this
+path is floating point; there is no integer/byte arithmetic to restate in C) in
+whatever dtype it is given, in the same order of operations as the reference's
+eager path, so a bf16 run reproduces the eager path's rounding points.
+
+Parity pin: ``tests/golden/*.npz`` hold outputs of the reference's own modules
+(``TriangleAttentionStartingNode``/``EndingNode`` with the VANILLA backend and
+``transition_mlp_w_norm_reference``) run on seeded inputs by
+``tests/golden/make_golden.py``; ``tests/test_oracle.py`` checks this file
+against them.
+
+Each function names the reference lines it restates (paths relative to the
+reference project root).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+STARTING = 0
+ENDING = 1
+
+
+@dataclass
+class NodeWeights:
+    """Parameters of one triangle-attention node, named as in the reference state_dict."""
+
+    ln_w: torch.Tensor  # layer_norm.weight [c]
+    ln_b: torch.Tensor  # layer_norm.bias [c]
+    w_bias: torch.Tensor  # pair_bias_proj.weight [H, c]
+    w_in: torch.Tensor  # mha.in_proj.weight [4*H*d, c] rows q,k,v,g
+    b_in: torch.Tensor | None  # mha.in_proj.bias [4*H*d] or None
+    w_out: torch.Tensor  # mha.o_proj.weight [c, H*d]
+    b_out: torch.Tensor | None  # mha.o_proj.bias [c] or None
+
+    def to(self, dtype: torch.dtype) -> "NodeWeights":
+        return NodeWeights(*[None if t is None else t.to(dtype) for t in
+                             (self.ln_w, self.ln_b, self.w_bias, self.w_in, self.b_in, self.w_out, self.b_out)])
+
+
+@dataclass
+class TransitionWeights:
+    ln_w: torch.Tensor  # norm.weight [c]
+    ln_b: torch.Tensor  # norm.bias [c]
+    w1: torch.Tensor  # fused_fc2_fc1.weight [2*hidden, c]: value rows, then gate rows
+    w2: torch.Tensor  # fc3.weight [c, hidden]
+
+    def to(self, dtype: torch.dtype) -> "TransitionWeights":
+        return TransitionWeights(*[t.to(dtype) for t in (self.ln_w, self.ln_b, self.w1, self.w2)])
+
+
+def make_node_weights(seed: int, c: int = 128, heads: int = 4, d: int = 32, std: float = 0.02,
+                      gate_bias: float | None = None, identity_ln: bool = True,
+                      out_bias: bool = False) -> NodeWeights:
+    """Seeded weights in the recipe of the reference's test helper ``init_module_weights``
+    (tests/_torch/__init__.py:33-63): matrices ~N(0, std²), 1-D weights 1, biases 0."""
+    g = torch.Generator().manual_seed(seed)
+    w_bias = torch.randn(heads, c, generator=g) * std
+    w_in = torch.randn(4 * heads * d, c, generator=g) * std
+    w_out = torch.randn(c, heads * d, generator=g) * std
+    if identity_ln:
+        ln_w, ln_b = torch.ones(c), torch.zeros(c)
+    else:
+        ln_w = 1 + 0.2 * torch.randn(c, generator=g)
+        ln_b = 0.2 * torch.randn(c, generator=g)
+    b_in = None
+    if gate_bias is not None:
+        b_in = torch.zeros(4 * heads * d)
+        b_in[3 * heads * d:] = gate_bias
+    b_out = 0.1 * torch.randn(c, generator=g) if out_bias else None
+    return NodeWeights(ln_w, ln_b, w_bias, w_in, b_in, w_out, b_out)
+
+
+def make_transition_weights(seed: int, c: int = 128, hidden: int = 512, std: float = 0.02,
+                            identity_ln: bool = True) -> TransitionWeights:
+    g = torch.Generator().manual_seed(seed)
+    w1 = torch.randn(2 * hidden, c, generator=g) * std
+    w2 = torch.randn(c, hidden, generator=g) * std
+    if identity_ln:
+        ln_w, ln_b = torch.ones(c), torch.zeros(c)
+    else:
+        ln_w = 1 + 0.2 * torch.randn(c, generator=g)
+        ln_b = 0.2 * torch.randn(c, generator=g)
+    return TransitionWeights(ln_w, ln_b, w1, w2)
+
+
+def additive_mask_bias(mask: torch.Tensor, inf: float, dtype: torch.dtype) -> torch.Tensor:
+    """``inf * (mask - 1)`` shaped [B, R, 1, 1, S].
+    Reference: _default_precompute_pair_masks, bionemo_ir/_torch/attention_backend/utils.py:305-317."""
+    m = mask.to(dtype)
+    return (inf * (m - 1))[..., :, None, None, :]
+
+
+def row_lengths(mask: torch.Tensor) -> torch.Tensor:
+    """int32 count of valid keys per row.
+    Reference: _cutedsl_precompute_pair_masks, bionemo_ir/_torch/attention_backend/utils.py:339-386."""
+    return (mask > 0.5).sum(dim=-1).to(torch.int32)
+
+
+def node_stages(z: torch.Tensor, mask: torch.Tensor | None, w: NodeWeights, node_type: int = STARTING,
+                heads: int = 4, inf: float = 1e9, transposed_bias: bool = False, eps: float = 1e-5) -> dict:
+    """Every intermediate of one node, in kernel order ([B, R, S, ...]; the ending node's R is z's second
+    pair axis).
+
+    Reference: TriangleAttentionNode.forward / _norm_and_bias (bionemo_ir/_torch/layers/triangle_nodes.py:223-265),
+    TriangleAttention._attend (bionemo_ir/_torch/layers/attention.py:257-296) and the VANILLA backend
+    (bionemo_ir/_torch/attention_backend/triangle_attention/vanilla.py:58-73).
+    """
+    dtype = w.ln_w.dtype
+    x = z.to(dtype)
+    ending = node_type == ENDING
+    xt = x.transpose(1, 2) if ending else x  # the node works on the transposed view
+    B, R, S, c = xt.shape
+    d = w.w_in.shape[0] // (4 * heads)
+    normed = F.layer_norm(xt, (c,), w.ln_w, w.ln_b, eps)
+    tb = F.linear(normed, w.w_bias)  # [B, R, S, H]
+    if transposed_bias:
+        tb = tb.transpose(1, 2)
+    tb = tb.permute(0, 3, 1, 2)  # [B, H, q, k]
+    if mask is None:
+        mask = xt.new_ones(B, R, S)
+    elif ending:
+        mask = mask.transpose(1, 2)
+    mb = additive_mask_bias(mask, inf, dtype)  # [B, R, 1, 1, S]
+    proj = F.linear(normed, w.w_in, w.b_in)
+    q, k, v, g = proj.split(heads * d, dim=-1)
+
+    def heads_first(t):  # [B, R, S, H*d] -> [B, R, H, S, d]
+        return t.reshape(B, R, S, heads, d).permute(0, 1, 3, 2, 4)
+
+    qh, kh, vh = heads_first(q), heads_first(k), heads_first(v)
+    a = torch.matmul(qh, kh.transpose(-1, -2))  # [B, R, H, S, S]
+    a = a / math.sqrt(d)
+    a = a + mb
+    a = a + tb.unsqueeze(1)
+    p = F.softmax(a, dim=-1)
+    o = torch.matmul(p, vh)  # [B, R, H, S, d]
+    o = o.transpose(-3, -2).reshape(B, R, S, heads * d)
+    og = o * torch.sigmoid(g)
+    update = F.linear(og, w.w_out, w.b_out)
+    return {"x": xt, "normed": normed, "tri_bias": tb, "q": q, "k": k, "v": v, "g": g, "logits": a, "o": o,
+            "og": og, "update": update, "mask": mask}
+
+
+def node_forward(z: torch.Tensor, mask: torch.Tensor | None, w: NodeWeights, node_type: int = STARTING, *,
+                 residual: bool = False, **kw) -> torch.Tensor:
+    """Output of the node in the caller's layout [B, I, J, c] (update, or z + update)."""
+    st = node_stages(z, mask, w, node_type, **kw)
+    out = st["x"] + st["update"] if residual else st["update"]
+    return out.transpose(1, 2) if node_type == ENDING else out
+
+
+def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bias: torch.Tensor, lengths: torch.Tensor,
+                   scale: float, empty_rows: str = "zeros") -> tuple[torch.Tensor, torch.Tensor]:
+    """Length-masked attention with its log-sum-exp, fp32.
+
+    q,k,v: [BR, S, H, d]; bias: [B, H, S, S]; lengths: [BR] int.  Keys t >= len are excluded; a row with
+    len == 0 gives zeros and lse = -inf ("zeros") or the mean of v over all keys ("uniform").
+    Reference: the compact reference of tests/_torch/test_triangle_attention_sm100_tail.py:55-66 and the
+    empty-row assertions at lines 99-101.
+    """
+    BR, S, H, d = q.shape
+    B = bias.shape[0]
+    R = BR // B
+    s = torch.einsum("nqhd,nkhd->nhqk", q.float(), k.float()) * scale
+    s = s + bias.float().repeat_interleave(R, dim=0)
+    key = torch.arange(S)
+    valid = key[None, :] < lengths.reshape(-1, 1).long()  # [BR, S]
+    s = s.masked_fill(~valid[:, None, None, :], float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)  # [BR, H, S]
+    p = torch.exp(s - lse.unsqueeze(-1))
+    p = torch.nan_to_num(p, nan=0.0)
+    o = torch.einsum("nhqk,nkhd->nqhd", p, v.float())
+    empty = lengths.reshape(-1) == 0
+    if empty.any() and empty_rows == "uniform":
+        o[empty] = v.float()[empty].mean(dim=1, keepdim=True).expand(-1, S, -1, -1)
+    return o, lse.permute(0, 2, 1)  # lse [BR, S, H]
+
+
+def transition_forward(x: torch.Tensor, mask: torch.Tensor | None, w: TransitionWeights, *, residual: bool = False,
+                       eps: float = 1e-5) -> torch.Tensor:
+    """``[x +] mask * fc3(silu(gate) * value)`` with ``[value|gate] = LN(x) @ w1.T``.
+
+    Reference: Transition._forward_impl (bionemo_ir/_torch/layers/transition.py:323-336), the SwiGLU of
+    bionemo_ir/dsl_kernels/triton/fused_swiglu.py:78-82 (silu computed in fp32 and rounded to the activation dtype
+    before the multiply) and transition_mlp_w_norm_reference
+    (bionemo_ir/_torch/custom_ops/transition_mlp_w_norm/ops.py:305-338).
+    """
+    dtype = w.ln_w.dtype
+    xd = x.to(dtype)
+    normed = F.layer_norm(xd, (xd.shape[-1],), w.ln_w, w.ln_b, eps)
+    h = F.linear(normed, w.w1)
+    value, gate = h.chunk(2, dim=-1)
+    act = F.silu(gate.float()).to(dtype) * value
+    y = F.linear(act, w.w2)
+    if mask is not None:
+        m = mask if mask.dim() == y.dim() else mask.unsqueeze(-1)
+        y = y * m.to(dtype)
+    return xd + y if residual else y
