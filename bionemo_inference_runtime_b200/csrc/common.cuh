@@ -264,6 +264,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// Same, into elements [OFF, OFF+32) of a 128-float register array.
+template <int OFF>
+__device__ __forceinline__ void tmem_ld32_f128(uint32_t taddr, float (&r)[128]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+      "%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=f"(r[OFF + 0]), "=f"(r[OFF + 1]), "=f"(r[OFF + 2]), "=f"(r[OFF + 3]), "=f"(r[OFF + 4]),
+        "=f"(r[OFF + 5]), "=f"(r[OFF + 6]), "=f"(r[OFF + 7]), "=f"(r[OFF + 8]), "=f"(r[OFF + 9]),
+        "=f"(r[OFF + 10]), "=f"(r[OFF + 11]), "=f"(r[OFF + 12]), "=f"(r[OFF + 13]), "=f"(r[OFF + 14]),
+        "=f"(r[OFF + 15]), "=f"(r[OFF + 16]), "=f"(r[OFF + 17]), "=f"(r[OFF + 18]), "=f"(r[OFF + 19]),
+        "=f"(r[OFF + 20]), "=f"(r[OFF + 21]), "=f"(r[OFF + 22]), "=f"(r[OFF + 23]), "=f"(r[OFF + 24]),
+        "=f"(r[OFF + 25]), "=f"(r[OFF + 26]), "=f"(r[OFF + 27]), "=f"(r[OFF + 28]), "=f"(r[OFF + 29]),
+        "=f"(r[OFF + 30]), "=f"(r[OFF + 31])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -273,6 +290,21 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+// Warp-collective TMEM store, the mirror of tmem_ld32.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+      "%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

@@ -1,0 +1,172 @@
+"""Generates the golden fixtures in this directory from the reference's own modules.
+
+Run where the reference checkout is available (it is not on the GPU machine):
+
+    BIOIR_REFERENCE=/path/to/reference python tests/golden/make_golden.py
+
+The reference package cannot be imported normally without its compiled kernel
+library, so this script pre-registers an empty ``bionemo_ir`` package object
+that points at the checkout, stubs the optional ``lru`` module, constructs the
+layers with ``skip_create_weights=True`` and assigns CPU parameters.  Only the
+reference's eager path runs (``attn_backend="VANILLA"``); the Transition's
+Triton SwiGLU, which has no CPU implementation, is replaced by the equivalent
+two PyTorch lines, and ``transition_mlp_w_norm_reference`` is called as is.
+
+Every fixture stores its inputs, weights and the reference outputs, so the
+tests need nothing but numpy to read them.
+"""
+
+from __future__ import annotations
+
+import collections
+import os
+import sys
+import types
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+REF = Path(os.environ.get("BIOIR_REFERENCE", "/root/reference"))
+sys.dont_write_bytecode = True
+
+
+def install_shim() -> None:
+    pkg = types.ModuleType("bionemo_ir")
+    pkg.__path__ = [str(REF / "bionemo_ir")]
+    pkg.CACHE_DIR = "/tmp/bioir_cache"
+    pkg.EXAMPLES_DIR = str(REF / "examples")
+    sys.modules["bionemo_ir"] = pkg
+    lru = types.ModuleType("lru")
+
+    class LRU(collections.OrderedDict):
+        def __init__(self, size, callback=None):
+            super().__init__()
+
+    lru.LRU = LRU
+    sys.modules["lru"] = lru
+
+
+def set_linear(linear, weight: torch.Tensor, bias: torch.Tensor | None) -> None:
+    linear.weight = torch.nn.Parameter(weight.clone(), requires_grad=False)
+    if bias is not None:
+        linear.bias = torch.nn.Parameter(bias.clone(), requires_grad=False)
+    else:
+        linear.register_parameter("bias", None)
+    linear._weights_created = True
+
+
+def build_node(cls, w: dict, dtype: torch.dtype, gate_bias: bool, out_bias: bool, **kw):
+    flags = {"q": False, "k": False, "v": False, "g": gate_bias, "o": out_bias}
+    node = cls(128, 32, 4, dtype=dtype, skip_create_weights=True, attn_backend="VANILLA", mha_bias_flags=flags, **kw)
+    node.layer_norm.weight.data.copy_(w["ln_w"])
+    node.layer_norm.bias.data.copy_(w["ln_b"])
+    set_linear(node.pair_bias_proj, w["w_bias"].to(dtype), None)
+    set_linear(node.mha.in_proj, w["w_in"].to(dtype), w["b_in"].to(dtype) if gate_bias else None)
+    set_linear(node.mha.o_proj, w["w_out"].to(dtype), w["b_out"].to(dtype) if out_bias else None)
+    return node.to(dtype)
+
+
+def node_weights(seed: int, identity_ln: bool) -> dict:
+    g = torch.Generator().manual_seed(seed)
+    w = {
+        "w_bias": torch.randn(4, 128, generator=g) * 0.02,
+        "w_in": torch.randn(512, 128, generator=g) * 0.02,
+        "w_out": torch.randn(128, 128, generator=g) * 0.02,
+        "ln_w": torch.ones(128) if identity_ln else 1 + 0.2 * torch.randn(128, generator=g),
+        "ln_b": torch.zeros(128) if identity_ln else 0.2 * torch.randn(128, generator=g),
+        "b_in": torch.zeros(512),
+        "b_out": 0.1 * torch.randn(128, generator=g),
+    }
+    w["b_in"][384:] = 1.0  # gate bias = 1
+    # keep everything exactly representable in bf16 so bf16 and fp32 runs share inputs
+    return {k: v.bfloat16().float() for k, v in w.items()}
+
+
+def save(name: str, **arrays) -> None:
+    out = {k: (v.float().numpy() if isinstance(v, torch.Tensor) else np.asarray(v)) for k, v in arrays.items()}
+    np.savez_compressed(HERE / f"{name}.npz", **out)
+    print(f"wrote {name}.npz ({(HERE / f'{name}.npz').stat().st_size / 1024:.0f} KiB)")
+
+
+def main() -> None:
+    install_shim()
+    from bionemo_ir._torch.custom_ops.transition_mlp_w_norm import transition_mlp_w_norm_reference
+    from bionemo_ir._torch.layers.transition import Transition
+    from bionemo_ir._torch.layers.triangle_nodes import TriangleAttentionEndingNode, TriangleAttentionStartingNode
+
+    torch.manual_seed(0)
+    # ---- case 1: starting node, all-ones mask, gate bias 1, identity LayerNorm (BASELINE config 1, shrunk)
+    g = torch.Generator().manual_seed(1000)
+    N = 24
+    z = torch.randn(1, N, N, 128, generator=g).bfloat16().float()
+    w = node_weights(1, identity_ln=True)
+    node = build_node(TriangleAttentionStartingNode, w, torch.float32, gate_bias=True, out_bias=False)
+    mask = torch.ones(1, N, N)
+    out_update = node(z, mask=mask)
+    out_res = node(z, mask=mask, residual=True)
+    save("node_start_fullmask", z=z, mask=mask, out_update=out_update, out_residual=out_res,
+         **{f"w_{k}": v for k, v in w.items()}, gate_bias=1, out_bias=0, node_type=0)
+
+    # ---- case 2: ending node, batch of 2 with different valid lengths (padded rows present), affine LayerNorm,
+    #      o_proj bias; fp32 and bf16 runs of the reference
+    g = torch.Generator().manual_seed(1001)
+    N = 20
+    z = torch.randn(2, N, N, 128, generator=g).bfloat16().float()
+    w = node_weights(2, identity_ln=False)
+    m = torch.zeros(2, N)
+    m[0, :13] = 1
+    m[1, :N] = 1
+    mask = m[:, :, None] * m[:, None, :]
+    node = build_node(TriangleAttentionEndingNode, w, torch.float32, gate_bias=True, out_bias=True)
+    out32 = node(z, mask=mask, residual=True)
+    node16 = build_node(TriangleAttentionEndingNode, w, torch.bfloat16, gate_bias=True, out_bias=True)
+    out16 = node16(z.bfloat16(), mask=mask.bfloat16(), residual=True)
+    start = build_node(TriangleAttentionStartingNode, w, torch.float32, gate_bias=True, out_bias=True)
+    out_start = start(z, mask=mask, residual=True)
+    save("node_end_padded", z=z, mask=mask, out_residual=out32, out_residual_bf16=out16, out_start_residual=out_start,
+         **{f"w_{k}": v for k, v in w.items()}, gate_bias=1, out_bias=1, node_type=1)
+
+    # ---- case 3: transposed triangle bias (OpenFold-3 ending node)
+    node_t = build_node(TriangleAttentionEndingNode, w, torch.float32, gate_bias=True, out_bias=True, transposed_bias=True)
+    out_t = node_t(z, mask=mask, residual=False)
+    save("node_end_transposed_bias", z=z, mask=mask, out_update=out_t, **{f"w_{k}": v for k, v in w.items()},
+         gate_bias=1, out_bias=1, node_type=1)
+
+    # ---- case 4: transition
+    g = torch.Generator().manual_seed(1002)
+    x = torch.randn(2, 12, 12, 128, generator=g).bfloat16().float()
+    tw = {
+        "w1": (torch.randn(1024, 128, generator=g) * 0.02).bfloat16().float(),
+        "w2": (torch.randn(128, 512, generator=g) * 0.02).bfloat16().float(),
+        "ln_w": (1 + 0.2 * torch.randn(128, generator=g)).bfloat16().float(),
+        "ln_b": (0.2 * torch.randn(128, generator=g)).bfloat16().float(),
+    }
+    tmask = (torch.rand(2, 12, 12, generator=g) > 0.3).float()
+    ref_res = transition_mlp_w_norm_reference(x, tmask, tw["ln_w"], tw["ln_b"], tw["w1"], None, tw["w2"], None, 1e-5,
+                                              activation="silu_gate", residual=True)
+    ref_upd = transition_mlp_w_norm_reference(x, None, tw["ln_w"], tw["ln_b"], tw["w1"], None, tw["w2"], None, 1e-5,
+                                              activation="silu_gate", residual=False)
+    layer = Transition(128, 512, dtype=torch.float32, skip_create_weights=True)
+    layer.norm.weight.data.copy_(tw["ln_w"])
+    layer.norm.bias.data.copy_(tw["ln_b"])
+    set_linear(layer.fused_fc2_fc1, tw["w1"], None)
+    set_linear(layer.fc3, tw["w2"], None)
+    layer._swiglu = lambda t: torch.nn.functional.silu(t[..., 512:]) * t[..., :512]
+    mod_upd = layer._forward_impl(x, tmask)
+    layer16 = Transition(128, 512, dtype=torch.bfloat16, skip_create_weights=True)
+    layer16.norm.weight.data.copy_(tw["ln_w"])
+    layer16.norm.bias.data.copy_(tw["ln_b"])
+    layer16 = layer16.to(torch.bfloat16)
+    set_linear(layer16.fused_fc2_fc1, tw["w1"].bfloat16(), None)
+    set_linear(layer16.fc3, tw["w2"].bfloat16(), None)
+    layer16._swiglu = lambda t: torch.nn.functional.silu(t[..., 512:].float()).to(t.dtype) * t[..., :512]
+    mod_upd16 = layer16._forward_impl(x.bfloat16(), tmask.bfloat16())
+    save("transition", x=x, mask=tmask, out_residual_masked=ref_res, out_update=ref_upd, out_module_update_masked=mod_upd,
+         out_module_update_masked_bf16=mod_upd16, **{f"w_{k}": v for k, v in tw.items()})
+
+
+if __name__ == "__main__":
+    with torch.no_grad():
+        main()

@@ -1,0 +1,29 @@
+"""Test helpers: golden-fixture loading and oracle weight conversion."""
+
+from __future__ import annotations
+
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from oracle import triangle_oracle as orc
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def load_golden(name: str) -> dict:
+    with np.load(GOLDEN / f"{name}.npz") as f:
+        return {k: (torch.from_numpy(f[k]) if f[k].ndim else f[k].item()) for k in f.files}
+
+
+def golden_node_weights(g: dict, dtype=torch.float32) -> orc.NodeWeights:
+    return orc.NodeWeights(
+        ln_w=g["w_ln_w"], ln_b=g["w_ln_b"], w_bias=g["w_w_bias"], w_in=g["w_w_in"],
+        b_in=g["w_b_in"] if g["gate_bias"] else None, w_out=g["w_w_out"],
+        b_out=g["w_b_out"] if g["out_bias"] else None,
+    ).to(dtype)
+
+
+def golden_transition_weights(g: dict, dtype=torch.float32) -> orc.TransitionWeights:
+    return orc.TransitionWeights(g["w_ln_w"], g["w_ln_b"], g["w_w1"], g["w_w2"]).to(dtype)

@@ -1,0 +1,79 @@
+"""Pins the CPU oracle against outputs of the reference's own modules (tests/golden/*.npz)."""
+
+import torch
+
+from oracle import triangle_oracle as orc
+from tests.helpers import golden_node_weights, golden_transition_weights, load_golden
+
+
+def test_start_node_full_mask_fp32():
+    g = load_golden("node_start_fullmask")
+    w = golden_node_weights(g)
+    upd = orc.node_forward(g["z"], g["mask"], w, orc.STARTING)
+    res = orc.node_forward(g["z"], g["mask"], w, orc.STARTING, residual=True)
+    assert (upd - g["out_update"]).abs().max() < 1e-6
+    assert (res - g["out_residual"]).abs().max() < 1e-6
+
+
+def test_end_node_padded_rows_fp32():
+    g = load_golden("node_end_padded")
+    w = golden_node_weights(g)
+    res = orc.node_forward(g["z"], g["mask"], w, orc.ENDING, residual=True)
+    assert (res - g["out_residual"]).abs().max() < 1e-6
+    start = orc.node_forward(g["z"], g["mask"], w, orc.STARTING, residual=True)
+    assert (start - g["out_start_residual"]).abs().max() < 1e-6
+
+
+def test_end_node_padded_rows_bf16_matches_eager_rounding():
+    g = load_golden("node_end_padded")
+    w = golden_node_weights(g, torch.bfloat16)
+    res = orc.node_forward(g["z"].bfloat16(), g["mask"].bfloat16(), w, orc.ENDING, residual=True)
+    # same ops in the same order on the same machine type; allow one bf16 ulp at |x| < 8
+    assert (res.float() - g["out_residual_bf16"]).abs().max() <= 2 ** -5
+
+
+def test_ending_is_transposed_starting():
+    g = load_golden("node_end_padded")
+    w = golden_node_weights(g)
+    end = orc.node_forward(g["z"], g["mask"], w, orc.ENDING)
+    start_t = orc.node_forward(g["z"].transpose(1, 2), g["mask"].transpose(1, 2), w, orc.STARTING).transpose(1, 2)
+    assert torch.equal(end, start_t)
+
+
+def test_transposed_bias():
+    g = load_golden("node_end_transposed_bias")
+    w = golden_node_weights(g)
+    upd = orc.node_forward(g["z"], g["mask"], w, orc.ENDING, transposed_bias=True)
+    assert (upd - g["out_update"]).abs().max() < 1e-6
+
+
+def test_empty_rows_are_uniform_in_the_eager_path():
+    """A row without a valid key averages V over every key (the additive -1e9 swamps the logits)."""
+    g = load_golden("node_end_padded")
+    w = golden_node_weights(g)
+    st = orc.node_stages(g["z"], g["mask"], w, orc.ENDING)
+    B, R, S, _ = st["v"].shape
+    lengths = orc.row_lengths(st["mask"])
+    assert (lengths == 0).any()
+    v = st["v"].reshape(B * R, S, 4, 32)
+    o_uniform, _ = orc.attention_core(st["q"].reshape(B * R, S, 4, 32), st["k"].reshape(B * R, S, 4, 32), v,
+                                      st["tri_bias"], lengths.reshape(-1), 32 ** -0.5, empty_rows="uniform")
+    assert (o_uniform.reshape(B, R, S, 128) - st["o"]).abs().max() < 1e-5
+
+
+def test_transition_fp32():
+    g = load_golden("transition")
+    w = golden_transition_weights(g)
+    res = orc.transition_forward(g["x"], g["mask"], w, residual=True)
+    upd = orc.transition_forward(g["x"], None, w)
+    mod = orc.transition_forward(g["x"], g["mask"], w)
+    assert (res - g["out_residual_masked"]).abs().max() < 1e-5
+    assert (upd - g["out_update"]).abs().max() < 1e-5
+    assert (mod - g["out_module_update_masked"]).abs().max() < 1e-5
+
+
+def test_transition_bf16_matches_eager_rounding():
+    g = load_golden("transition")
+    w = golden_transition_weights(g, torch.bfloat16)
+    mod = orc.transition_forward(g["x"].bfloat16(), g["mask"].bfloat16(), w)
+    assert (mod.float() - g["out_module_update_masked_bf16"]).abs().max() <= 2 ** -8
