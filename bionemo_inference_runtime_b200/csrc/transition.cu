@@ -1,0 +1,390 @@
+// Pair transition for sm_100a: out = [x +] mask * ( (silu(gate) * value) · W2ᵀ ),
+// [value|gate] = LayerNorm(x) · W1ᵀ, hidden 512, one kernel, hidden kept on chip.
+//
+// A persistent CTA per SM walks 128-row tiles of x.  The hidden dimension is cut in
+// 8 chunks of 64 units; for each chunk
+//   GEMM1  acc1[128 x (64 value | 64 gate)] = x_tile · W1chunkᵀ   (tcgen05, K = 128, raw bf16 rows of x;
+//          LayerNorm is folded into W1 and finished in the epilogue with the row's mean / rstd)
+//   SwiGLU one thread per row: TMEM -> registers, value/gate affine, silu via tanh, product -> bf16
+//          tile H in shared memory (K-major, 128-byte swizzle = A operand of the next GEMM)
+//   GEMM2  acc2[128 x 128] += H · W2chunkᵀ                        (tcgen05, K = 64)
+// W1/W2 chunks stream from L2 through two TMA rings; GEMM1 of chunk j+1 is issued before
+// GEMM2 of chunk j so the tensor core runs while the SwiGLU warps work.
+//
+// Warp roles (384 threads): warps 0-3 / 4-7 SwiGLU + output warpgroups (even / odd chunks),
+// warp 8 TMA producer, warp 9 MMA issuer / TMEM owner, warps 10-11 idle.
+#include "common.cuh"
+#include "layout.h"
+
+namespace b200ta {
+namespace {
+
+constexpr int kThreads = 384;
+constexpr int kTileM = 128;
+constexpr int kChunk = 64;                 // hidden units per chunk
+constexpr int kChunks = kHidden / kChunk;  // 8
+
+struct TransParams {
+  long long rows;
+  int num_tiles;
+  const float2* sc;  // [1024] {rowsum, const} of the folded W1 rows
+  const __nv_bfloat16* mask;
+  float eps;
+  int add_residual;
+  int* status;
+};
+
+// shared memory map
+constexpr int kSmX = 0;                        // 2 x 32 KiB
+constexpr int kSmW1 = kSmX + 2 * 32768;        // 2 x 32 KiB: [k-half][64 value rows | 64 gate rows][64 ch]
+constexpr int kSmW2 = kSmW1 + 2 * 32768;       // 2 x 16 KiB: [128 out rows][64 hidden]
+constexpr int kSmH = kSmW2 + 2 * 16384;        // 2 x 16 KiB: [128 rows][64 hidden]
+constexpr int kSmOut = kSmH + 2 * 16384;       // 8 warps x 2 KiB staging slabs
+constexpr int kSmBars = kSmOut + 8 * 2048;
+constexpr int kSmTotal = kSmBars + 256;
+constexpr int kSmDynamic = kSmTotal + 1024;
+
+enum Bar {
+  X_FULL = 0, X_EMPTY = 2, W1_FULL = 4, W1_EMPTY = 6, W2_FULL = 8, W2_EMPTY = 10,
+  ACC1_FULL = 12, ACC1_FREE = 14, H_FULL = 16, H_FREE = 18, ACC2_FULL = 20, ACC2_FREE = 22, NUM_BARS = 24
+};
+
+constexpr uint32_t kTmemAcc1 = 0, kTmemAcc2 = 256, kTmemCols = 512;
+
+__global__ void __launch_bounds__(kThreads, 1)
+transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w1,
+                  const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_out,
+                  const TransParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + kSmBars;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kSmBars + NUM_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + kSmBars + NUM_BARS * 8 + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bars + (X_FULL + i) * 8, 1);
+      mbar_init(bars + (X_EMPTY + i) * 8, 9);  // GEMM1 commit + 8 epilogue warps
+      mbar_init(bars + (W1_FULL + i) * 8, 1);
+      mbar_init(bars + (W1_EMPTY + i) * 8, 1);
+      mbar_init(bars + (W2_FULL + i) * 8, 1);
+      mbar_init(bars + (W2_EMPTY + i) * 8, 1);
+      mbar_init(bars + (ACC1_FULL + i) * 8, 1);
+      mbar_init(bars + (ACC1_FREE + i) * 8, 4);
+      mbar_init(bars + (H_FULL + i) * 8, 4);
+      mbar_init(bars + (H_FREE + i) * 8, 1);
+      mbar_init(bars + (ACC2_FULL + i) * 8, 1);
+      mbar_init(bars + (ACC2_FREE + i) * 8, 8);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 9) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int my_tiles = (p.num_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_x);
+      tma_prefetch_desc(&tm_w1);
+      tma_prefetch_desc(&tm_w2);
+      tma_prefetch_desc(&tm_out);
+      bool ok = true;
+      int c = 0;  // chunk counter
+      for (int i = 0; ok && i < my_tiles; ++i) {
+        const int tile = blockIdx.x + i * gridDim.x;
+        const int xs = i & 1;
+        ok = mbar_wait(bars + (X_EMPTY + xs) * 8, ((i >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(bars + (X_FULL + xs) * 8, 32768);
+        tma_load_2d(base + kSmX + xs * 32768, &tm_x, bars + (X_FULL + xs) * 8, 0, tile * kTileM);
+        tma_load_2d(base + kSmX + xs * 32768 + 16384, &tm_x, bars + (X_FULL + xs) * 8, 64, tile * kTileM);
+        for (int j = 0; j < kChunks; ++j, ++c) {
+          const int st = c & 1;
+          const uint32_t par = ((c >> 1) & 1) ^ 1;
+          ok = mbar_wait(bars + (W1_EMPTY + st) * 8, par, abort_flag);
+          if (!ok) break;
+          const uint32_t f1 = bars + (W1_FULL + st) * 8;
+          mbar_expect_tx(f1, 32768);
+          for (int kh = 0; kh < 2; ++kh) {
+            const uint32_t dst = base + kSmW1 + st * 32768 + kh * 16384;
+            tma_load_2d(dst, &tm_w1, f1, kh * 64, j * kChunk);                  // value rows
+            tma_load_2d(dst + 8192, &tm_w1, f1, kh * 64, kHidden + j * kChunk);  // gate rows
+          }
+          ok = mbar_wait(bars + (W2_EMPTY + st) * 8, par, abort_flag);
+          if (!ok) break;
+          const uint32_t f2 = bars + (W2_FULL + st) * 8;
+          mbar_expect_tx(f2, 16384);
+          tma_load_2d(base + kSmW2 + st * 16384, &tm_w2, f2, j * kChunk, 0);
+        }
+      }
+      if (*abort_flag && c > 0) {
+        const int last = c - 1;
+        mbar_wait(bars + (W2_FULL + (last & 1)) * 8, (last >> 1) & 1, abort_flag + 1);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(kTileM, 128);
+      bool ok = true;
+      int c1 = 0, c2 = 0;  // GEMM1 / GEMM2 chunk counters
+      for (int i = 0; ok && i < my_tiles; ++i) {
+        const int xs = i & 1;
+        ok = mbar_wait(bars + (X_FULL + xs) * 8, (i >> 1) & 1, abort_flag);
+        if (!ok) break;
+        for (int j = 0; ok && j <= kChunks; ++j) {
+          if (j < kChunks) {
+            const int e = c1 & 1;
+            const uint32_t par = (c1 >> 1) & 1;
+            ok = mbar_wait(bars + (W1_FULL + e) * 8, par, abort_flag) &&
+                 mbar_wait(bars + (ACC1_FREE + e) * 8, par ^ 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t a = base + kSmX + xs * 32768 + (k >> 2) * 16384 + (k & 3) * 32;
+              const uint32_t b = base + kSmW1 + e * 32768 + (k >> 2) * 16384 + (k & 3) * 32;
+              umma_ss(tmem_base + kTmemAcc1 + e * 128, make_smem_desc(a, 16, 1024, kLayoutSw128),
+                      make_smem_desc(b, 16, 1024, kLayoutSw128), idesc, k > 0 ? 1u : 0u);
+            }
+            umma_commit(bars + (ACC1_FULL + e) * 8);
+            umma_commit(bars + (W1_EMPTY + e) * 8);
+            if (j == kChunks - 1) umma_commit(bars + (X_EMPTY + xs) * 8);
+            ++c1;
+          }
+          if (j > 0) {
+            const int jj = j - 1;
+            const int e = c2 & 1;
+            const uint32_t par = (c2 >> 1) & 1;
+            ok = mbar_wait(bars + (W2_FULL + e) * 8, par, abort_flag) &&
+                 mbar_wait(bars + (H_FULL + e) * 8, par, abort_flag);
+            if (ok && jj == 0) ok = mbar_wait(bars + (ACC2_FREE + (i & 1)) * 8, ((i >> 1) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t a = base + kSmH + e * 16384 + k * 32;
+              const uint32_t b = base + kSmW2 + e * 16384 + k * 32;
+              umma_ss(tmem_base + kTmemAcc2 + (i & 1) * 128, make_smem_desc(a, 16, 1024, kLayoutSw128),
+                      make_smem_desc(b, 16, 1024, kLayoutSw128), idesc, (jj > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(bars + (W2_EMPTY + e) * 8);
+            umma_commit(bars + (H_FREE + e) * 8);
+            if (jj == kChunks - 1) umma_commit(bars + (ACC2_FULL + (i & 1)) * 8);
+            ++c2;
+          }
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ SwiGLU / output warpgroups
+    const int e = warp >> 2;               // chunk parity and output column half this warpgroup owns
+    const int m = (warp & 3) * 32 + lane;  // row inside the tile == TMEM lane
+    const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
+    const uint32_t slab = base + kSmOut + warp * 2048;
+    bool ok = true;
+    int n = 0;  // uses of this warpgroup's acc1 / H buffers
+    for (int i = 0; ok && i < my_tiles; ++i) {
+      const int tile = blockIdx.x + i * gridDim.x;
+      const int xs = i & 1;
+      const long long row = (long long)tile * kTileM + m;
+      ok = mbar_wait(bars + (X_FULL + xs) * 8, (i >> 1) & 1, abort_flag);
+      if (!ok) break;
+      // LayerNorm statistics of row m
+      const uint32_t x0 = base + kSmX + xs * 32768;
+      float rstd, nmr;
+      {
+        uint32_t v[64];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          uint4 x = lds128(x0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
+          v[c * 4 + 0] = x.x, v[c * 4 + 1] = x.y, v[c * 4 + 2] = x.z, v[c * 4 + 3] = x.w;
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) sum += bf16_lo(v[j]) + bf16_hi(v[j]);
+        const float mu = sum * (1.f / kC);
+        float var = 0.f;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const float d0 = bf16_lo(v[j]) - mu, d1 = bf16_hi(v[j]) - mu;
+          var = fmaf(d0, d0, var);
+          var = fmaf(d1, d1, var);
+        }
+        rstd = rsqrtf(var * (1.f / kC) + p.eps);
+        nmr = -mu * rstd;
+      }
+      for (int j = e; ok && j < kChunks; j += 2, ++n) {
+        ok = mbar_wait(bars + (ACC1_FULL + e) * 8, n & 1, abort_flag) &&
+             mbar_wait(bars + (H_FREE + e) * 8, (n & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const float2* scv = p.sc + j * kChunk;            // value rows of this chunk
+        const float2* scg = p.sc + kHidden + j * kChunk;  // gate rows
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t av[32], ag[32];
+          tmem_ld32(lane_taddr + kTmemAcc1 + e * 128 + half * 32, av);
+          tmem_ld32(lane_taddr + kTmemAcc1 + e * 128 + 64 + half * 32, ag);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            float hid[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int col = half * 32 + 2 * t + u;
+              const float2 sv = __ldg(scv + col), sg = __ldg(scg + col);
+              const float val = fmaf(rstd, __uint_as_float(av[2 * t + u]), fmaf(nmr, sv.x, sv.y));
+              const float h = fmaf(rstd, __uint_as_float(ag[2 * t + u]), fmaf(nmr, sg.x, sg.y));  // gate / 2
+              hid[u] = fmaf(h, tanh_approx(h), h) * val;  // silu(gate) * value
+            }
+            pk[t] = pack_bf16x2(hid[0], hid[1]);
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            sts128(base + kSmH + e * 16384 + sw128_offset(m, half * 4 + c),
+                   make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]));
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bars + (ACC1_FREE + e) * 8);
+          mbar_arrive(bars + (H_FULL + e) * 8);
+        }
+      }
+      if (!ok) break;
+      // ---- output: columns [64e, 64e+64) of acc2 (+ residual) (* mask)
+      const int ab = i & 1;
+      ok = mbar_wait(bars + (ACC2_FULL + ab) * 8, (i >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      float mk = 1.f;
+      if (p.mask != nullptr && row < p.rows) mk = __bfloat162float(p.mask[row]);
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        uint32_t a[32];
+        tmem_ld32(lane_taddr + kTmemAcc2 + ab * 128 + e * 64 + g * 32, a);
+        tmem_ld_wait();
+        uint32_t res[16];
+        if (p.add_residual) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 x = lds128(x0 + e * 16384 + sw128_offset(m, g * 4 + c));
+            res[c * 4 + 0] = x.x, res[c * 4 + 1] = x.y, res[c * 4 + 2] = x.z, res[c * 4 + 3] = x.w;
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) res[t] = 0u;
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t)
+          pk[t] = pack_bf16x2(fmaf(mk, __uint_as_float(a[2 * t]), bf16_lo(res[t])),
+                              fmaf(mk, __uint_as_float(a[2 * t + 1]), bf16_hi(res[t])));
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          sts128(slab + sw64_offset(lane, c), make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]));
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const long long row0 = (long long)tile * kTileM + (warp & 3) * 32;
+          if (row0 < p.rows) tma_store_2d(&tm_out, slab, e * 64 + g * 32, int(row0));
+          tma_store_commit();
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bars + (ACC2_FREE + ab) * 8);
+        mbar_arrive(bars + (X_EMPTY + xs) * 8);
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) *p.status = B200TA_ERR_DEVICE_WAIT;
+}
+
+}  // namespace
+}  // namespace b200ta
+
+extern "C" {
+
+int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* packed, float eps, void* out,
+                      int64_t os, int64_t rows, int add_residual, void* stream) {
+  using namespace b200ta;
+  B200TA_REQUIRE(x && packed && out, "transition: NULL pointer");
+  B200TA_REQUIRE(rows > 0 && rows < (int64_t(1) << 31), "transition: rows=%lld out of range", (long long)rows);
+  B200TA_REQUIRE(xs >= kC && xs % 8 == 0 && os >= kC && os % 8 == 0, "transition: row strides must be >= 128 and multiples of 8 elements");
+  B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "transition: packed must be 256-byte aligned");
+  DeviceState* st = nullptr;
+  int rc = get_device_state(&st);
+  if (rc != B200TA_OK) return rc;
+  const char* pk = static_cast<const char*>(packed);
+
+  CUtensorMap tm_x, tm_w1, tm_w2, tm_out;
+  {
+    uint64_t dims[2] = {uint64_t(kC), uint64_t(rows)};
+    uint64_t strides[1] = {uint64_t(xs) * 2};
+    uint32_t box[2] = {64, 128};
+    rc = encode_tensor_map(&tm_x, x, 2, 2, dims, strides, box, SWZ_128, "transition x");
+    if (rc != B200TA_OK) return rc;
+    uint64_t ostrides[1] = {uint64_t(os) * 2};
+    uint32_t obox[2] = {32, 32};
+    rc = encode_tensor_map(&tm_out, out, 2, 2, dims, ostrides, obox, SWZ_64, "transition out");
+    if (rc != B200TA_OK) return rc;
+  }
+  {
+    uint64_t dims[2] = {uint64_t(kC), uint64_t(kTransRows)};
+    uint64_t strides[1] = {uint64_t(kC) * 2};
+    uint32_t box[2] = {64, 64};
+    rc = encode_tensor_map(&tm_w1, pk + kTransW1Off, 2, 2, dims, strides, box, SWZ_128, "transition w1");
+    if (rc != B200TA_OK) return rc;
+  }
+  {
+    uint64_t dims[2] = {uint64_t(kHidden), uint64_t(kC)};
+    uint64_t strides[1] = {uint64_t(kHidden) * 2};
+    uint32_t box[2] = {64, 128};
+    rc = encode_tensor_map(&tm_w2, pk + kTransW2Off, 2, 2, dims, strides, box, SWZ_128, "transition w2");
+    if (rc != B200TA_OK) return rc;
+  }
+
+  TransParams p{};
+  p.rows = rows;
+  p.num_tiles = int((rows + kTileM - 1) / kTileM);
+  p.sc = reinterpret_cast<const float2*>(pk + kTransScOff);
+  p.mask = static_cast<const __nv_bfloat16*>(mask);
+  p.eps = eps;
+  p.add_residual = add_residual ? 1 : 0;
+  p.status = st->status_dev;
+
+  B200TA_CHECK_CUDA(cudaFuncSetAttribute(transition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmDynamic));
+  const int grid = p.num_tiles < st->num_sms ? p.num_tiles : st->num_sms;
+  transition_kernel<<<grid, kThreads, kSmDynamic, static_cast<cudaStream_t>(stream)>>>(tm_x, tm_w1, tm_w2, tm_out, p);
+  B200TA_CHECK_CUDA(cudaGetLastError());
+  return B200TA_OK;
+}
+
+}  // extern "C"
