@@ -1,0 +1,353 @@
+"""Benchmark of the triangle-attention hot path (starting node, then ending node) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2|cfg3|n768]
+
+One "step" is one pass of the hot path over one batch of synthetic pair tensors: the starting-node and the
+ending-node TriangleAttention (LayerNorm, q/k/v/gate + triangle-bias projections, masked biased attention, sigmoid
+gate, output projection, residual) applied in sequence; workloads with a transition also run the fused pair
+transition.  Default workload ("cfg2"): z[1, 512, 512, 128] bf16, 475 valid tokens, weights ~N(0, 0.02²).
+
+Metric: tri-attn TFLOP/s = algorithmic flops of the step (valid positions only) / time.  Rank 0 prints one JSON
+line.  `value` is timed with CUDA events with inputs resident in HBM and L2 flushed between steps; `e2e` runs the
+same step through the module API from pinned host memory and back.  With N > 1 every rank processes its own batch
+(independent pair tensors, no data-path collective): weak scaling.
+
+--impl reference times the CPU restatement of the reference's eager path (oracle/) on the host cores, on a
+bounded row sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (batch, tokens, valid-length spec, transition?)
+    "cfg2": dict(B=1, N=512, valid="475", transition=False,
+                 desc="start+end TriangleAttention, z[1,512,512,128] bf16, 475 valid tokens (BASELINE config 2)"),
+    "cfg3": dict(B=64, N=256, valid="U160-256", transition=True,
+                 desc="start+end TriangleAttention + transition, z[64,256,256,128] bf16, valid ~U{160..256} (BASELINE config 3)"),
+    "n768": dict(B=1, N=768, valid="768", transition=True,
+                 desc="start+end TriangleAttention + transition, z[1,768,768,128] bf16, all valid (pair track of BASELINE config 4)"),
+}
+
+
+def valid_lengths(spec: str, B: int, N: int, gen: torch.Generator) -> list[int]:
+    if spec.startswith("U"):
+        lo, hi = map(int, spec[1:].split("-"))
+        return torch.randint(lo, hi + 1, (B,), generator=gen).tolist()
+    return [int(spec)] * B
+
+
+def node_flops(L: int) -> float:
+    """Algorithmic flops of one node for an item with L valid tokens: L² positions x (projections + 512·L)."""
+    return float(L) * L * (164864.0 + 512.0 * L)
+
+
+def attention_core_flops(L: int) -> float:
+    return float(L) * L * 512.0 * L
+
+
+def transition_flops(L: int) -> float:
+    return float(L) * L * 393216.0
+
+
+def measured_peaks() -> tuple[float, float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[tuple[float, float, str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i",
+                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                f = [x.strip() for x in out.split(",")]
+                reasons = [n for n, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                              "sw_power_cap"), f[2:6]) if v == "Active"]
+                self.samples.append((float(f[0]), float(f[1]), ",".join(reasons)))
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        reasons = sorted({r for s in self.samples for r in s[2].split(",") if r})
+        return {"sm_mhz": statistics.median(s[0] for s in self.samples), "sm_max_mhz": self.samples[0][1],
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def make_inputs(cfg: dict, seed: int, device):
+    from oracle import triangle_oracle as orc  # weight recipe only (seeded generators); nothing is computed with it
+
+    gen = torch.Generator().manual_seed(seed)
+    B, N = cfg["B"], cfg["N"]
+    z = torch.randn(B, N, N, 128, generator=gen).to(torch.bfloat16)
+    lens = valid_lengths(cfg["valid"], B, N, gen)
+    m = torch.zeros(B, N)
+    for b, L in enumerate(lens):
+        m[b, :L] = 1
+    mask = m[:, :, None] * m[:, None, :]
+    w_start = orc.make_node_weights(seed + 1)
+    w_end = orc.make_node_weights(seed + 2)
+    w_tr = orc.make_transition_weights(seed + 3)
+    return z, mask, lens, w_start, w_end, w_tr
+
+
+def build_modules(w_start, w_end, w_tr, device):
+    import bionemo_inference_runtime_b200 as b200
+
+    def node(cls, w):
+        n = cls(128, 32, 4, dtype=torch.bfloat16, attn_backend="Heuristic")
+        n.load_state_dict({"layer_norm.weight": w.ln_w, "layer_norm.bias": w.ln_b, "pair_bias_proj.weight": w.w_bias,
+                           "mha.in_proj.weight": w.w_in, "mha.o_proj.weight": w.w_out}, strict=True)
+        return n.to(device)
+
+    start = node(b200.TriangleAttentionStartingNode, w_start)
+    end = node(b200.TriangleAttentionEndingNode, w_end)
+    tr = b200.Transition(128, 512, dtype=torch.bfloat16)
+    tr.load_state_dict({"norm.weight": w_tr.ln_w, "norm.bias": w_tr.ln_b, "fused_fc2_fc1.weight": w_tr.w1,
+                        "fc3.weight": w_tr.w2}, strict=True)
+    return start, end, tr.to(device)
+
+
+def run_ours(args) -> dict:
+    import torch.distributed as dist
+
+    from bionemo_inference_runtime_b200 import _lib, ops
+    import bionemo_inference_runtime_b200 as b200
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    cfg = WORKLOADS[args.workload]
+    z_host, mask_host, lens, w_start, w_end, w_tr = make_inputs(cfg, 1000 + rank, device)
+    start, end, trans = build_modules(w_start, w_end, w_tr, device)
+    pre = b200.precompute_pair_masks("Heuristic", mask_host.to(device))
+    z_dev = z_host.to(device)
+    bufs: dict = {}
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+
+    def step(z):
+        z1 = start(z, mask_bias=pre.mask_bias, buffers=bufs, residual=True)
+        z2 = end(z1, mask_bias=pre.mask_bias_transposed, buffers=bufs, residual=True, inplace_residual=True)
+        if cfg["transition"]:
+            z2 = trans(z2, residual=True, inplace=True)
+        return z2
+
+    launches_per_step = 6 + (1 if cfg["transition"] else 0)
+    flops_step = sum(2 * node_flops(L) + (transition_flops(L) if cfg["transition"] else 0.0) for L in lens)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ---------------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step(z_dev)
+    barrier()
+    times = []
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        for _ in range(args.steps):
+            flush.fill_(1)  # evict L2 (126 MB) between timed steps
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step(z_dev)
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+        barrier()
+    ms = sum(times) / len(times)
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel abandoned a bounded wait during the benchmark")
+
+    # ---- end to end: pinned host -> device -> step -> pinned host ----------------------------------------
+    z_pin = z_host.pin_memory()
+    out_pin = torch.empty_like(z_pin).pin_memory()
+    e2e_times = []
+    for i in range(3 + args.steps):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        zd = z_pin.to(device, non_blocking=True)
+        out_pin.copy_(step(zd), non_blocking=True)
+        torch.cuda.synchronize()
+        if i >= 3:
+            e2e_times.append((time.perf_counter() - t0) * 1e3)
+    e2e_ms = sum(e2e_times) / len(e2e_times)
+
+    # ---- per-kernel timing of the dominant kernel (attention core), live, with CUDA events ------------------
+    B, N = cfg["B"], cfg["N"]
+    packed = start._packed(device)
+    qkvg, bias = ops.prologue(z_dev, packed)
+    og = torch.empty(B, N, N, 128, dtype=torch.bfloat16, device=device)
+    ktimes = []
+    for i in range(3 + args.steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.attention(qkvg, bias, pre.mask_bias, B, N, N, out=og)
+        e1.record()
+        e1.synchronize()
+        if i >= 3:
+            ktimes.append(e0.elapsed_time(e1))
+    attn_ms = sum(ktimes) / len(ktimes)
+    attn_flops = sum(attention_core_flops(L) for L in lens)
+    peak_tf, peak_gbs, peak_kind = measured_peaks()
+
+    # ---- aggregate over ranks ------------------------------------------------------------------------------
+    stats = torch.tensor([ms, e2e_ms, attn_ms], dtype=torch.float64, device=device)
+    total_flops = torch.tensor([flops_step], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(total_flops, op=dist.ReduceOp.SUM)
+    ms, e2e_ms, attn_ms = stats.tolist()
+    flops_all = total_flops.item()
+    bytes_io = z_host.numel() * 2
+
+    result = {
+        "metric": "tri_attn_tflops", "value": flops_all / ms / 1e9, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}", "per_gpu_batch": cfg["B"], "tokens": cfg["N"],
+                   "valid_lengths": cfg["valid"], "l2": "flushed between timed steps (256 MiB write)",
+                   "empty_row_mode": "uniform", "parallelism": f"independent batches x{world}"},
+        "e2e": {"value": flops_all / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": bytes_io, "d2h_bytes_per_step": bytes_io},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"kernel": "attention_kernel", "bound": "tensor", "achieved": attn_flops / attn_ms / 1e9,
+                     "peak": peak_tf, "unit": "TFLOP/s", "frac": attn_flops / attn_ms / 1e9 / peak_tf,
+                     "peak_source": f"{peak_kind} bf16 burst", "ms_per_launch": attn_ms, "traffic": TRAFFIC.get(args.workload)},
+        "clocks": clocks.summary(),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(cfg, args.workload)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per attention launch, from the committed ncu summaries (profiles/)
+TRAFFIC: dict[str, float | None] = {"cfg2": None, "cfg3": None, "n768": None}
+
+
+def cpu_sample(cfg: dict, rows: int, threads: int):
+    """Times the oracle (CPU restatement of the reference's eager path, fp32) on a row sample of the workload."""
+    from oracle import triangle_oracle as orc
+
+    torch.set_num_threads(threads)
+    z, mask, lens, w_start, w_end, w_tr = make_inputs(cfg, 1000, "cpu")
+    B, N = cfg["B"], cfg["N"]
+    items = min(B, 2)
+    z, mask = z[:items].float(), mask[:items]
+    rows = min(rows, N)
+    sel = torch.linspace(0, max(lens[0] - 1, 0), rows).long().unique()  # valid rows of the first item, spread out
+
+    t0 = time.perf_counter()
+    orc.node_forward_rows(z, mask, w_start, orc.STARTING, sel, residual=True)
+    orc.node_forward_rows(z, mask, w_end, orc.ENDING, sel, residual=True)
+    if cfg["transition"]:
+        orc.transition_forward(z[:, sel], None, w_tr, residual=True)
+    dt = time.perf_counter() - t0
+    # flops of the sample: rows x valid columns of each sampled item (LayerNorm/bias of unsampled rows earn nothing)
+    fl = 0.0
+    for b in range(items):
+        L = lens[b]
+        r = int((sel < L).sum())
+        fl += 2 * r * L * (164864.0 + 512.0 * L) + (r * L * 393216.0 if cfg["transition"] else 0.0)
+    return fl, dt, len(sel), items
+
+
+def cpu_baseline(cfg: dict, name: str, rows: int = 96) -> dict:
+    threads = os.cpu_count() or 1
+    fl, dt, nrows, items = cpu_sample(cfg, rows, threads)
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "seconds": dt,
+            "sample": f"{name}: {nrows} of {cfg['N']} pair rows of {items} item(s), both nodes"
+                      f"{' + transition' if cfg['transition'] else ''}, fp32 eager restatement (oracle/), torch CPU"}
+
+
+def run_reference(args) -> dict:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return {}
+    cfg = WORKLOADS[args.workload]
+    threads = os.cpu_count() or 1
+    for _ in range(min(args.warmup, 1)):
+        cpu_sample(cfg, 32, threads)
+    fl = dt = 0.0
+    nrows = items = 0
+    for _ in range(args.steps):
+        f, d, nrows, items = cpu_sample(cfg, 48, threads)
+        fl += f
+        dt += d
+    value = fl / dt / 1e12
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    sample = (f"{args.workload}: {nrows} of {cfg['N']} pair rows of {items} item(s) per step, both nodes"
+              f"{' + transition' if cfg['transition'] else ''}, fp32 eager restatement (oracle/), torch CPU")
+    return {"impl": "reference", "metric": "tri_attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {cfg['desc']}", "sampled": sample},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if result:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

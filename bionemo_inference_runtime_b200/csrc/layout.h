@@ -16,7 +16,8 @@ constexpr size_t kNodeWOff = 0;                                   // bf16 [528][
 constexpr size_t kNodeScOff = kNodeWOff + size_t(kNodeRows) * kC * 2;  // float2 [528] {rowsum, const}
 constexpr size_t kNodeWoOff = kNodeScOff + size_t(kNodeRows) * 8;      // bf16 [128][128] (o_proj)
 constexpr size_t kNodeBoOff = kNodeWoOff + size_t(kC) * kC * 2;        // float [128]
-constexpr size_t kNodePackBytes = ((kNodeBoOff + kC * 4 + 255) / 256) * 256;
+constexpr size_t kNodeFlagsOff = kNodeBoOff + kC * 4;                  // int [4]: {input is layer-normalised by the kernel, 0, 0, 0}
+constexpr size_t kNodePackBytes = ((kNodeFlagsOff + 16 + 255) / 256) * 256;
 
 // ---- transition ---------------------------------------------------------------
 // Rows of the folded first linear: value(512) then gate(512, pre-halved for the
@@ -25,6 +26,7 @@ constexpr int kTransRows = 2 * kHidden;
 constexpr size_t kTransW1Off = 0;                                         // bf16 [1024][128]
 constexpr size_t kTransScOff = kTransW1Off + size_t(kTransRows) * kC * 2; // float2 [1024]
 constexpr size_t kTransW2Off = kTransScOff + size_t(kTransRows) * 8;      // bf16 [128][512]
-constexpr size_t kTransPackBytes = ((kTransW2Off + size_t(kC) * kHidden * 2 + 255) / 256) * 256;
+constexpr size_t kTransFlagsOff = kTransW2Off + size_t(kC) * kHidden * 2;   // int [4], as above
+constexpr size_t kTransPackBytes = ((kTransFlagsOff + 16 + 255) / 256) * 256;
 
 }  // namespace b200ta

@@ -25,7 +25,7 @@ __device__ __forceinline__ float load_w(const void* p, int dtype, size_t i) {
 __global__ void fold_rows_kernel(const void* wa, int rows_a, const void* wb, int rows_b,
                                  const void* bias_a, const void* gamma, const void* beta, int dtype,
                                  int scale_from, int scale_to, float scale, __nv_bfloat16* wp,
-                                 float2* sc) {
+                                 float2* sc, int* flags) {
   const int n = blockIdx.x;
   const int c = threadIdx.x;
   __shared__ float red[3][4];
@@ -39,8 +39,11 @@ __global__ void fold_rows_kernel(const void* wa, int rows_a, const void* wb, int
   const float s = (n >= scale_from && n < scale_to) ? scale : 1.f;
   w *= s;
   b *= s;
-  const float g = load_w(gamma, dtype, c);
-  const float be = load_w(beta, dtype, c);
+  // gamma == NULL: the input is already normalised; plain projection, no centring
+  const bool normalize = gamma != nullptr;
+  const float g = normalize ? load_w(gamma, dtype, c) : 1.f;
+  const float be = normalize ? load_w(beta, dtype, c) : 0.f;
+  if (n == 0 && c == 0) flags[0] = normalize ? 1 : 0;
   float wg = w * g;
   float cterm = w * be;
   // block reductions over the 128 channels
@@ -50,7 +53,7 @@ __global__ void fold_rows_kernel(const void* wa, int rows_a, const void* wb, int
     __syncthreads();
     return red[slot][0] + red[slot][1] + red[slot][2] + red[slot][3];
   };
-  const float mean = block_sum(wg, 0) * (1.f / kC);
+  const float mean = normalize ? block_sum(wg, 0) * (1.f / kC) : 0.f;
   const float csum = block_sum(cterm, 1);
   const __nv_bfloat16 q = __float2bfloat16_rn(wg - mean);
   wp[size_t(n) * kC + c] = q;
@@ -85,7 +88,8 @@ int b200ta_pack_node_weights(const void* ln_w, const void* ln_b, const void* w_i
                              const void* w_bias, const void* w_out, const void* b_out,
                              int weight_dtype, void* packed, void* stream) {
   using namespace b200ta;
-  B200TA_REQUIRE(ln_w && ln_b && w_in && w_bias && w_out && packed, "pack_node_weights: NULL pointer");
+  B200TA_REQUIRE(w_in && w_bias && w_out && packed, "pack_node_weights: NULL pointer");
+  B200TA_REQUIRE((ln_w == nullptr) == (ln_b == nullptr), "pack_node_weights: pass both LayerNorm vectors or neither");
   B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "pack_node_weights: packed must be 256-byte aligned");
   int rc = check_dtype(weight_dtype);
   if (rc != B200TA_OK) return rc;
@@ -95,7 +99,7 @@ int b200ta_pack_node_weights(const void* ln_w, const void* ln_b, const void* w_i
   fold_rows_kernel<<<kNodeRows, kC, 0, s>>>(
       w_in, 4 * kHeads * kHeadDim, w_bias, kHeads, b_in, ln_w, ln_b, weight_dtype, 4 * kHeads * kHeadDim,
       4 * kHeads * kHeadDim + kHeads, kLog2e, reinterpret_cast<__nv_bfloat16*>(base + kNodeWOff),
-      reinterpret_cast<float2*>(base + kNodeScOff));
+      reinterpret_cast<float2*>(base + kNodeScOff), reinterpret_cast<int*>(base + kNodeFlagsOff));
   convert_kernel<<<(kC * kC + 255) / 256, 256, 0, s>>>(w_out, weight_dtype, size_t(kC) * kC,
                                                        reinterpret_cast<__nv_bfloat16*>(base + kNodeWoOff), nullptr);
   convert_kernel<<<1, kC, 0, s>>>(b_out, weight_dtype, kC, nullptr, reinterpret_cast<float*>(base + kNodeBoOff));
@@ -106,7 +110,8 @@ int b200ta_pack_node_weights(const void* ln_w, const void* ln_b, const void* w_i
 int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const void* w1, const void* w2,
                                    int weight_dtype, void* packed, void* stream) {
   using namespace b200ta;
-  B200TA_REQUIRE(ln_w && ln_b && w1 && w2 && packed, "pack_transition_weights: NULL pointer");
+  B200TA_REQUIRE(w1 && w2 && packed, "pack_transition_weights: NULL pointer");
+  B200TA_REQUIRE((ln_w == nullptr) == (ln_b == nullptr), "pack_transition_weights: pass both LayerNorm vectors or neither");
   B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "pack_transition_weights: packed must be 256-byte aligned");
   int rc = check_dtype(weight_dtype);
   if (rc != B200TA_OK) return rc;
@@ -115,7 +120,8 @@ int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const voi
   // gate rows are halved: silu(g) = h + h * tanh(h) with h = g / 2
   fold_rows_kernel<<<kTransRows, kC, 0, s>>>(w1, kTransRows, nullptr, 0, nullptr, ln_w, ln_b, weight_dtype, kHidden,
                                              kTransRows, 0.5f, reinterpret_cast<__nv_bfloat16*>(base + kTransW1Off),
-                                             reinterpret_cast<float2*>(base + kTransScOff));
+                                             reinterpret_cast<float2*>(base + kTransScOff),
+                                             reinterpret_cast<int*>(base + kTransFlagsOff));
   convert_kernel<<<(kC * kHidden + 255) / 256, 256, 0, s>>>(w2, weight_dtype, size_t(kC) * kHidden,
                                                             reinterpret_cast<__nv_bfloat16*>(base + kTransW2Off), nullptr);
   B200TA_CHECK_CUDA(cudaGetLastError());

@@ -28,6 +28,7 @@ struct TransParams {
   long long rows;
   int num_tiles;
   const float2* sc;  // [1024] {rowsum, const} of the folded W1 rows
+  const int* flags;  // flags[0] != 0 -> apply LayerNorm statistics
   const __nv_bfloat16* mask;
   float eps;
   int add_residual;
@@ -203,8 +204,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       if (!ok) break;
       // LayerNorm statistics of row m
       const uint32_t x0 = base + kSmX + xs * 32768;
-      float rstd, nmr;
-      {
+      float rstd = 1.f, nmr = 0.f;
+      if (__ldg(p.flags) != 0) {
         uint32_t v[64];
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
@@ -375,6 +376,7 @@ int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* p
   p.rows = rows;
   p.num_tiles = int((rows + kTileM - 1) / kTileM);
   p.sc = reinterpret_cast<const float2*>(pk + kTransScOff);
+  p.flags = reinterpret_cast<const int*>(pk + kTransFlagsOff);
   p.mask = static_cast<const __nv_bfloat16*>(mask);
   p.eps = eps;
   p.add_residual = add_residual ? 1 : 0;

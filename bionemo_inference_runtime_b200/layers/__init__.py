@@ -1,0 +1,21 @@
+"""Module-level API: the reference's pair-track layers on the sm_100a kernels."""
+
+from .attention_backend import (AttentionBackend, AttentionMetadata, AttentionType, B200TriangleAttention,
+                                PrecomputedPairMasks, create_attention, get_attention_backend, mask_to_lengths,
+                                precompute_pair_masks, register_precompute_pair_masks)
+from .auto_chunk import (CHUNK_REGISTRY, PAIR_TRANSITION, TRIANGLE_ATTENTION, ChunkPolicy, chunk_apply,
+                         default_autochunk_min, iter_chunks)
+from .buffers import PreallocatedBuffers, ensure_buffer
+from .linear import Linear, WeightMode, WeightsLoadingConfig
+from .transition import Transition
+from .triangle_nodes import (TriangleAttention, TriangleAttentionEndingNode, TriangleAttentionNode,
+                             TriangleAttentionNodeType, TriangleAttentionStartingNode, split_pair_bias_proj)
+
+__all__ = [
+    "AttentionBackend", "AttentionMetadata", "AttentionType", "B200TriangleAttention", "PrecomputedPairMasks",
+    "create_attention", "get_attention_backend", "mask_to_lengths", "precompute_pair_masks",
+    "register_precompute_pair_masks", "CHUNK_REGISTRY", "PAIR_TRANSITION", "TRIANGLE_ATTENTION", "ChunkPolicy",
+    "chunk_apply", "default_autochunk_min", "iter_chunks", "PreallocatedBuffers", "ensure_buffer", "Linear",
+    "WeightMode", "WeightsLoadingConfig", "Transition", "TriangleAttention", "TriangleAttentionEndingNode",
+    "TriangleAttentionNode", "TriangleAttentionNodeType", "TriangleAttentionStartingNode", "split_pair_bias_proj",
+]

@@ -58,7 +58,7 @@ def pack_node_weights(ln_w, ln_b, w_in, b_in, w_bias, w_out, b_out) -> torch.Ten
             f"pair_bias_proj {tuple(ts[4].shape)}, o_proj {tuple(ts[5].shape)}"
         )
     dt = _weight_dtype(*ts)
-    packed = torch.empty(_lib.load().b200ta_node_pack_bytes(), dtype=torch.uint8, device=ts[0].device)
+    packed = torch.empty(_lib.load().b200ta_node_pack_bytes(), dtype=torch.uint8, device=ts[2].device)
     _lib.call("b200ta_pack_node_weights", *[_ptr(t) for t in ts], dt, packed.data_ptr(), _stream())
     return packed
 
@@ -69,7 +69,7 @@ def pack_transition_weights(ln_w, ln_b, w1, w2) -> torch.Tensor:
     if tuple(ts[2].shape) != (2 * HIDDEN, C) or tuple(ts[3].shape) != (C, HIDDEN):
         raise ValueError(f"kernel is specialised for dim={C}, hidden={HIDDEN}: got {tuple(ts[2].shape)}, {tuple(ts[3].shape)}")
     dt = _weight_dtype(*ts)
-    packed = torch.empty(_lib.load().b200ta_transition_pack_bytes(), dtype=torch.uint8, device=ts[0].device)
+    packed = torch.empty(_lib.load().b200ta_transition_pack_bytes(), dtype=torch.uint8, device=ts[2].device)
     _lib.call("b200ta_pack_transition_weights", *[_ptr(t) for t in ts], dt, packed.data_ptr(), _stream())
     return packed
 
@@ -104,7 +104,8 @@ def prologue(z, packed, eps: float = 1e-5, *, ending: bool = False, want_qkvg: b
     if want_bias and bias is None:
         if R != S:
             raise ValueError("the triangle bias needs a square pair tensor")
-        bias = torch.empty((B, HEADS, R, S_pad), dtype=torch.bfloat16, device=z.device)
+        alloc = torch.zeros if transposed_bias else torch.empty
+        bias = alloc((B, HEADS, R, S_pad), dtype=torch.bfloat16, device=z.device)
     if qkvg is not None:
         qs = (qkvg.stride(0), qkvg.stride(1), qkvg.stride(2), qkvg.stride(3))
     else:
@@ -116,7 +117,9 @@ def prologue(z, packed, eps: float = 1e-5, *, ending: bool = False, want_qkvg: b
     else:
         bs = (0, 0, 0, 0)
     _lib.call("b200ta_prologue", z.data_ptr(), sb, sr, ss, packed.data_ptr(), float(eps), _ptr(qkvg), *qs,
-              1 if want_qkvg else 0, _ptr(bias if want_bias else None), *bs, B, R, S, S_pad, _stream())
+              1 if want_qkvg else 0, _ptr(bias if want_bias else None), *bs, B, R, S,
+              S if transposed_bias else S_pad,  # transposed: the key padding lies along the other axis; no zero fill
+              _stream())
     return qkvg, bias
 
 

@@ -159,6 +159,42 @@ def node_forward(z: torch.Tensor, mask: torch.Tensor | None, w: NodeWeights, nod
     return out.transpose(1, 2) if node_type == ENDING else out
 
 
+def node_forward_rows(z: torch.Tensor, mask: torch.Tensor | None, w: NodeWeights, node_type: int, rows: torch.Tensor,
+                      *, residual: bool = False, heads: int = 4, inf: float = 1e9, eps: float = 1e-5) -> torch.Tensor:
+    """``node_forward`` restricted to the pair rows ``rows`` of the node's own row axis (second pair axis of ``z``
+    for the ending node): returns ``[B, len(rows), S, c]`` in kernel order.
+
+    A row's attention needs only that row of q/k/v/g plus the triangle bias of *all* rows, so sampled rows are exact
+    and cheap; large shapes are checked and timed through this function.  Same reference lines as ``node_stages``.
+    """
+    dtype = w.ln_w.dtype
+    x = z.to(dtype)
+    xt = x.transpose(1, 2) if node_type == ENDING else x
+    B, R, S, c = xt.shape
+    d = w.w_in.shape[0] // (4 * heads)
+    normed = F.layer_norm(xt, (c,), w.ln_w, w.ln_b, eps)
+    tb = F.linear(normed, w.w_bias).permute(0, 3, 1, 2)  # [B, H, q, k] from every row
+    if mask is None:
+        mask = xt.new_ones(B, R, S)
+    elif node_type == ENDING:
+        mask = mask.transpose(1, 2)
+    n_s, m_s, x_s = normed[:, rows], mask[:, rows], xt[:, rows]
+    r = n_s.shape[1]
+    proj = F.linear(n_s, w.w_in, w.b_in)
+    q, k, v, g = proj.split(heads * d, dim=-1)
+
+    def heads_first(t):
+        return t.reshape(B, r, S, heads, d).permute(0, 1, 3, 2, 4)
+
+    a = torch.matmul(heads_first(q), heads_first(k).transpose(-1, -2))
+    a = a / math.sqrt(d)
+    a = a + additive_mask_bias(m_s, inf, dtype)
+    a = a + tb.unsqueeze(1)
+    o = torch.matmul(F.softmax(a, dim=-1), heads_first(v)).transpose(-3, -2).reshape(B, r, S, heads * d)
+    update = F.linear(o * torch.sigmoid(g), w.w_out, w.b_out)
+    return x_s + update if residual else update
+
+
 def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bias: torch.Tensor, lengths: torch.Tensor,
                    scale: float, empty_rows: str = "zeros") -> tuple[torch.Tensor, torch.Tensor]:
     """Length-masked attention with its log-sum-exp, fp32.

@@ -1,0 +1,121 @@
+"""Host-side logic that needs no GPU: chunking knobs, mask forms, weight loading, state_dict contract."""
+
+import pytest
+import torch
+
+import bionemo_inference_runtime_b200 as b200
+from bionemo_inference_runtime_b200.layers import auto_chunk
+
+
+def test_chunk_policy_thresholds_and_registry():
+    p = b200.ChunkPolicy(chunk_size=8, min_size=16, dim=1, min_rank=4)
+    assert not p.should_chunk(torch.zeros(1, 16, 16, 4))
+    assert p.should_chunk(torch.zeros(1, 17, 17, 4))
+    assert not p.should_chunk(torch.zeros(17, 17, 4))  # rank below min_rank
+    assert not p.replace(enabled=False).should_chunk(torch.zeros(1, 17, 17, 4))
+    assert b200.CHUNK_REGISTRY.get(b200.TRIANGLE_ATTENTION).chunk_size == 512
+    assert b200.CHUNK_REGISTRY.get(b200.PAIR_TRANSITION).dim == 1
+    assert auto_chunk.default_autochunk_min() >= 512
+    assert list(b200.iter_chunks(10, 4)) == [(0, 4), (4, 4), (8, 2)]
+
+
+def test_chunk_apply_matches_dense_call():
+    x = torch.randn(2, 20, 5, 3)
+    m = torch.randn(2, 20, 5)
+    policy = b200.ChunkPolicy(chunk_size=7, min_size=4, dim=1)
+    fn = lambda a, b, scale: a * b.unsqueeze(-1) * scale  # noqa: E731
+    assert torch.equal(b200.chunk_apply(fn, x, m, policy=policy, scale=2.0), fn(x, m, 2.0))
+
+
+def test_mask_forms_reduce_to_the_same_lengths():
+    m = torch.zeros(2, 6)
+    m[0, :4] = 1
+    m[1, :6] = 1
+    pair = m[:, :, None] * m[:, None, :]
+    add = b200.precompute_pair_masks("VANILLA", pair, inf=1e9, dtype=torch.float32)
+    cnt = b200.precompute_pair_masks("Heuristic", pair)
+    assert add.mask_bias.shape == (2, 6, 1, 1, 6) and cnt.mask_bias.dtype == torch.int32
+    assert torch.equal(b200.mask_to_lengths(add.mask_bias, 2, 6), cnt.mask_bias)
+    assert torch.equal(b200.mask_to_lengths(add.mask_bias_transposed, 2, 6), cnt.mask_bias_transposed)
+    assert torch.equal(b200.mask_to_lengths(cnt.mask_bias.reshape(-1), 2, 6), cnt.mask_bias)
+    per_item = torch.tensor([4, 6], dtype=torch.int32)
+    assert b200.mask_to_lengths(per_item, 2, 6).tolist() == [[4] * 6, [6] * 6]
+    with pytest.raises(ValueError):
+        b200.mask_to_lengths(torch.zeros(5, dtype=torch.int32), 2, 6)
+    with pytest.raises(ValueError):
+        b200.precompute_pair_masks("nope", pair)
+
+
+def test_every_reference_backend_name_is_accepted():
+    for name in ("VANILLA", "SDPA", "CUEQUIV", "CuTeDSL", "ClaudeKit", "Heuristic"):
+        assert b200.get_attention_backend(name) is b200.B200TriangleAttention
+    with pytest.raises(ValueError):
+        b200.get_attention_backend("FLASH")
+    with pytest.raises(ValueError):
+        b200.create_attention("VANILLA", 0, 8, 32)  # unsupported head count
+
+
+def test_state_dict_contract_of_the_node():
+    flags = {"q": False, "k": False, "v": False, "g": True, "o": True}
+    node = b200.TriangleAttentionEndingNode(128, 32, 4, dtype=torch.bfloat16, mha_bias_flags=flags)
+    sd = node.state_dict()
+    assert {k: tuple(v.shape) for k, v in sd.items()} == {
+        "layer_norm.weight": (128,), "layer_norm.bias": (128,), "pair_bias_proj.weight": (4, 128),
+        "mha.in_proj.weight": (512, 128), "mha.in_proj.bias": (512,), "mha.o_proj.weight": (128, 128),
+        "mha.o_proj.bias": (128,)}
+    assert node.node_type == b200.TriangleAttentionNodeType.ENDING
+    assert all(not p.requires_grad for n, p in node.named_parameters() if "layer_norm" not in n)
+    plain = b200.TriangleAttentionStartingNode(128, 32, 4, dtype=torch.bfloat16)
+    assert sorted(plain.state_dict()) == ["layer_norm.bias", "layer_norm.weight", "mha.in_proj.weight",
+                                          "mha.o_proj.weight", "pair_bias_proj.weight"]
+    node.load_state_dict(sd, strict=True)
+
+
+def test_state_dict_contract_of_the_transition():
+    t = b200.Transition(128, 512, dtype=torch.bfloat16)
+    assert {k: tuple(v.shape) for k, v in t.state_dict().items()} == {
+        "norm.weight": (128,), "norm.bias": (128,), "fused_fc2_fc1.weight": (1024, 128), "fc3.weight": (128, 512)}
+    assert sorted(b200.Transition(128, 512, dtype=torch.bfloat16, normalize=False).state_dict()) == [
+        "fc3.weight", "fused_fc2_fc1.weight"]
+    with pytest.raises(ValueError):
+        b200.Transition(256, 1024)
+
+
+def test_linear_fused_segment_loading():
+    lin = b200.Linear(8, 10, bias=True, dtype=torch.float32, weights_loading_config=b200.WeightsLoadingConfig(
+        weight_mode=b200.WeightMode.FUSED_SEGMENTS_LINEAR, segment_sizes=(4, 4, 2)))
+    segs = [{"weight": torch.ones(4, 8)}, {"weight": 2 * torch.ones(3, 8), "bias": torch.ones(3)},
+            {"weight": 3 * torch.ones(2, 8)}]
+    lin.load_weights(segs)
+    w = lin.weight.cpu()
+    assert torch.equal(w[:4], torch.ones(4, 8)) and torch.equal(w[4:7], 2 * torch.ones(3, 8))
+    assert torch.equal(w[7], torch.zeros(8)) and torch.equal(w[8:], 3 * torch.ones(2, 8))
+    assert lin.bias.cpu().tolist() == [0, 0, 0, 0, 1, 1, 1, 0, 0, 0]
+
+
+def test_split_pair_bias_proj_moves_the_fifth_segment():
+    weights = {"blocks.0.tri_attn_start.mha.in_proj": [{"weight": torch.zeros(128, 128)} for _ in range(4)]
+               + [{"weight": torch.ones(4, 128)}]}
+    out = b200.split_pair_bias_proj(weights)
+    assert len(out["blocks.0.tri_attn_start.mha.in_proj"]) == 4
+    assert torch.equal(out["blocks.0.tri_attn_start.pair_bias_proj"][0]["weight"], torch.ones(4, 128))
+
+
+def test_layers_refuse_cpu_tensors_and_other_dtypes():
+    node = b200.TriangleAttentionStartingNode(128, 32, 4, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA"):
+        node(torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="bfloat16"):
+        b200.TriangleAttentionStartingNode(128, 32, 4, dtype=torch.float32)(torch.zeros(1, 8, 8, 128))
+    with pytest.raises(ValueError):
+        b200.TriangleAttentionStartingNode(128, 32, 4, dtype=torch.bfloat16, pair_mask_left_aligned=False)
+    with pytest.raises(ValueError, match="CUDA"):
+        b200.Transition(128, 512, dtype=torch.bfloat16)(torch.zeros(4, 128, dtype=torch.bfloat16))
+
+
+def test_ensure_buffer_reuses_and_reallocates():
+    bufs: dict = {}
+    a = b200.ensure_buffer(bufs, "k", (2, 3), torch.float32, torch.device("cpu"))
+    assert b200.ensure_buffer(bufs, "k", (2, 3), torch.float32, torch.device("cpu")) is a
+    assert b200.ensure_buffer(bufs, "k", (2, 4), torch.float32, torch.device("cpu")) is not a
+    assert b200.ensure_buffer(None, "k", (2, 3), torch.float32, torch.device("cpu")) is None
