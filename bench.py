@@ -94,7 +94,7 @@ class ClockSampler:
                 self.samples.append((float(f[0]), float(f[1]), ",".join(reasons)))
             except Exception:
                 pass
-            self._stop.wait(0.1)
+            self._stop.wait(0.02)
 
     def __enter__(self):
         self._thread.start()
@@ -299,12 +299,18 @@ def cpu_sample(cfg: dict, rows: int, threads: int):
     return fl, dt, len(sel), items
 
 
-def cpu_baseline(cfg: dict, name: str, rows: int = 96) -> dict:
+def cpu_baseline(cfg: dict, name: str, rows: int = 128, budget_s: float = 12.0) -> dict:
+    """Repeats the row sample until about ``budget_s`` seconds of CPU work have been timed."""
     threads = os.cpu_count() or 1
-    fl, dt, nrows, items = cpu_sample(cfg, rows, threads)
+    cpu_sample(cfg, 16, threads)  # warm the thread pool and the allocator
+    fl = dt = 0.0
+    nrows = items = reps = 0
+    while dt < budget_s and reps < 64:
+        f, d, nrows, items = cpu_sample(cfg, rows, threads)
+        fl, dt, reps = fl + f, dt + d, reps + 1
     return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
             "seconds": dt,
-            "sample": f"{name}: {nrows} of {cfg['N']} pair rows of {items} item(s), both nodes"
+            "sample": f"{name}: {reps} x ({nrows} of {cfg['N']} pair rows of {items} item(s)), both nodes"
                       f"{' + transition' if cfg['transition'] else ''}, fp32 eager restatement (oracle/), torch CPU"}
 
 
@@ -338,7 +344,7 @@ def run_reference(args) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")

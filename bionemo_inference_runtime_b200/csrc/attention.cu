@@ -1,34 +1,38 @@
 // Triangle attention core for sm_100a: flash-style, head_dim 32, bf16 in, fp32 softmax.
 //
 // For every pair row (b, r), head h and query s:
-//   o[s,:] = softmax_t( scale * q[s]·k[t] + bias[b,h,s,t] ; t < len[b,r] ) · v[t,:]   (* sigmoid(gate[s,:]))
-// The N x N x N logits never exist in memory: a CTA owns 256 queries of one (b, r, h),
-// walks the keys in tiles of 128 and keeps running max / sum / output per query.
+//   o[s,:] = softmax_t( scale * (q[s]·k[t] + bias[b,h,s,t]) ; t < len[b,r] ) · v[t,:]   (* sigmoid(gate[s,:]))
+// where `bias` is the triangle bias already divided by `scale` (the prologue writes it that way).
+// The N x N x N logits never exist in memory: a CTA owns 256 queries of one (b, r, h), walks the
+// keys in tiles of 128 and keeps a running max / sum per query and the output in TMEM.
 //
-// Per key tile:
+// Everything that touches a score matrix element is either a tensor-core or a TMEM operation:
 //   TMA      K tile, V tile and the two 128x128 bias tiles (one per 128-query half) -> shared memory
-//   tcgen05  S = Q·Kᵀ        (128x128x32, both operands K-major in smem, accumulator in TMEM)
-//   softmax  one thread per query row: TMEM -> registers, logit = S*scale*log2e + bias (bias is
-//            stored pre-multiplied by log2e), running max, exp2, row sum; the bf16 probabilities
-//            overwrite the bias tile in place (same swizzled layout = the A operand of the next MMA)
-//   tcgen05  O_tile = P·V    (128x32x128, V is the MN-major B operand straight from its [key][d] tile)
-//   softmax  accumulates O_tile into registers with the usual rescale.
-// The two 128-query halves are handled by two softmax warpgroups that share K/V and
-// alternate on the tensor core, so one half's exponentials overlap the other's MMAs.
+//   tcgen05  S  = Q·Kᵀ          (128x128x32, K-major operands in smem, accumulator in TMEM)
+//   tcgen05  S += I·Bias        (128x128x128: the identity, resident in TMEM as the A operand, times the
+//                                bias tile as MN-major B operand - the bias add costs no CUDA-core work)
+//   softmax  one thread per query row: S from TMEM -> registers, running max (lazily updated), exp2,
+//            row sum; the bf16 probabilities go straight back to TMEM
+//   tcgen05  O += P·V           (128x32x128: P is the A operand from TMEM, V the MN-major B operand from
+//                                its [key][d] tile); O is only rescaled when the running max moved
+// The two 128-query halves are handled by two softmax warpgroups that share K/V and alternate on the
+// tensor core.  The MMA warp runs one key tile ahead (also across work items), so the next scores are
+// in TMEM before a warpgroup asks for them.
 //
-// Warp roles (384 threads): warps 0-3 softmax half 0, warps 4-7 softmax half 1,
-// warp 8 TMA producer, warp 9 MMA issuer / TMEM owner, warps 10-11 idle.  The third
-// warpgroup gives most of its registers to the softmax warpgroups (setmaxnreg).
+// Warp roles (384 threads): warps 0-3 softmax half 0, warps 4-7 softmax half 1, warp 8 TMA producer,
+// warp 9 score-MMA issuer / TMEM owner, warp 10 P·V-MMA issuer, warp 11 idle.  The third warpgroup gives most of its registers to
+// the softmax warpgroups (setmaxnreg).
 #include "common.cuh"
 #include "layout.h"
 
 namespace b200ta {
 namespace {
 
-constexpr int kThreads = 384;  // 3 warpgroups; the third holds the producer and MMA warps
-constexpr int kQTile = 128;   // queries per softmax warpgroup
-constexpr int kKTile = 128;   // keys per tile
+constexpr int kThreads = 384;
+constexpr int kQTile = 128;  // queries per softmax warpgroup
+constexpr int kKTile = 128;  // keys per tile
 constexpr int kStages = 2;
+constexpr float kRescaleThreshold = 8.f;  // log2 units: O is rescaled only when the max grew by more than 2^8
 
 struct AttnParams {
   int B, R, S, S_pad;
@@ -47,34 +51,41 @@ struct AttnParams {
 };
 
 // shared-memory map (bytes, relative to the 1024-aligned base)
-constexpr int kSmQ = 0;                          // 2 item buffers x 2 halves x 8 KiB
-constexpr int kSmStage = kSmQ + 2 * 2 * 8192;    // per stage: K 8 KiB, V 8 KiB, bias/P half0 32 KiB, half1 32 KiB
-constexpr int kStageBytes = 8192 + 8192 + 2 * 32768;
-constexpr int kSmBars = kSmStage + kStages * kStageBytes;
+// K and the bias tiles are only read by the score MMAs, which run a tile ahead, so their ring frees early
+// and two stages are enough to hide the load latency; V waits for the probabilities and gets a deeper ring.
+constexpr int kVStages = 4;
+constexpr int kSmQ = 0;                        // 2 item buffers x 2 halves x 8 KiB
+constexpr int kSmStage = kSmQ + 2 * 2 * 8192;  // per stage: K 8 KiB, bias half0 32 KiB, bias half1 32 KiB
+constexpr int kStageBytes = 8192 + 2 * 32768;
+constexpr int kSmV = kSmStage + kStages * kStageBytes;  // kVStages x 8 KiB
+constexpr int kSmBars = kSmV + kVStages * 8192;
 constexpr int kSmTotal = kSmBars + 256;
 constexpr int kSmDynamic = kSmTotal + 1024;
 
 enum Bar {
   Q_FULL = 0,    // [2] item buffer
   Q_EMPTY = 2,   // [2]
-  KV_FULL = 4,   // [kStages]
-  KV_EMPTY = 6,  // [kStages]
+  KB_FULL = 4,   // [kStages] K + bias
+  KB_EMPTY = 6,  // [kStages]
   S_FULL = 8,    // [2] per half
   S_FREE = 10,   // [2]
   P_FULL = 12,   // [2]
   O_FULL = 14,   // [2]
-  NUM_BARS = 16
+  V_FULL = 16,   // [kVStages]
+  V_EMPTY = 20,  // [kVStages]
+  NUM_BARS = 24
 };
 
-// TMEM columns: S of half w at w*128, PV tile of half w at 256 + w*32
-constexpr uint32_t kTmemS = 0, kTmemO = 256, kTmemCols = 512;
+// TMEM columns: S of half w | O of half w | P (bf16 pairs) of half w | identity (bf16 pairs)
+constexpr uint32_t kTmemS = 0, kTmemO = 256, kTmemP = 320, kTmemI = 448, kTmemCols = 512;
 
 struct Item {
   int b, r, h, q0, br;
-  int len;      // keys that take part (S for a uniform row)
-  int nkt;      // key tiles
-  bool uniform; // no valid key and "uniform" semantics: every logit equal
-  bool skip;    // no valid key and "zeros" semantics: nothing to compute
+  int len;       // keys that take part (S for a uniform row)
+  int nkt;       // key tiles
+  int nvalid;    // 128-query halves that hold at least one query
+  bool uniform;  // no valid key and "uniform" semantics: every logit equal
+  bool skip;     // no valid key and "zeros" semantics: nothing to compute
 };
 
 __device__ __forceinline__ Item decode_item(const AttnParams& p, int item) {
@@ -93,7 +104,43 @@ __device__ __forceinline__ Item decode_item(const AttnParams& p, int item) {
   it.skip = len == 0 && !p.empty_uniform;
   it.len = it.uniform ? p.S : len;
   it.nkt = (it.len + kKTile - 1) / kKTile;
+  it.nvalid = (it.q0 + kQTile < p.S) ? 2 : 1;
   return it;
+}
+
+// Walks the (item, key tile) sequence of one CTA in order, skipping items without work.
+struct TileCursor {
+  int i;     // index into this CTA's item list
+  int kt;    // key tile inside the item
+  int g;     // tiles before this one (ring position)
+  int qi;    // items with work before this one (Q buffer position)
+  Item it;
+  bool valid;
+};
+
+__device__ __forceinline__ void cursor_seek(const AttnParams& p, TileCursor& c, int my_items) {
+  // positions the cursor on the first item with work at or after c.i
+  while (c.i < my_items) {
+    c.it = decode_item(p, blockIdx.x + c.i * gridDim.x);
+    if (!c.it.skip) {
+      c.valid = true;
+      return;
+    }
+    ++c.i;
+  }
+  c.valid = false;
+}
+__device__ __forceinline__ void cursor_init(const AttnParams& p, TileCursor& c, int my_items) {
+  c.i = 0, c.kt = 0, c.g = 0, c.qi = 0;
+  cursor_seek(p, c, my_items);
+}
+__device__ __forceinline__ void cursor_next(const AttnParams& p, TileCursor& c, int my_items) {
+  ++c.g;
+  if (++c.kt < c.it.nkt) return;
+  c.kt = 0;
+  ++c.qi;
+  ++c.i;
+  cursor_seek(p, c, my_items);
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -116,12 +163,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + (Q_FULL + i) * 8, 1);
       mbar_init(bars + (Q_EMPTY + i) * 8, 1);
-      mbar_init(bars + (KV_FULL + i) * 8, 1);
-      mbar_init(bars + (KV_EMPTY + i) * 8, 1);
+      mbar_init(bars + (KB_FULL + i) * 8, 1);
+      mbar_init(bars + (KB_EMPTY + i) * 8, 1);
       mbar_init(bars + (S_FULL + i) * 8, 1);
       mbar_init(bars + (S_FREE + i) * 8, 4);
       mbar_init(bars + (P_FULL + i) * 8, 4);
       mbar_init(bars + (O_FULL + i) * 8, 1);
+    }
+    for (int i = 0; i < kVStages; ++i) {
+      mbar_init(bars + (V_FULL + i) * 8, 1);
+      mbar_init(bars + (V_EMPTY + i) * 8, 1);
     }
     fence_mbar_init();
   }
@@ -130,6 +181,24 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  // The 128x128 bf16 identity, A operand of the bias MMA: TMEM lane q, column c holds elements (q, 2c) and
+  // (q, 2c+1) as a bf16 pair, so lane q has a single 1.0 in column q/2.
+  if (warp < 4) {
+    const int q = warp * 32 + lane;
+    const uint32_t one = (q & 1) ? 0x3F800000u : 0x00003F80u;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t v[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = (half * 32 + c == (q >> 1)) ? one : 0u;
+      tmem_st32(tmem_base + (uint32_t(warp * 32) << 16) + kTmemI + half * 32, v);
+    }
+    tmem_st_wait();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
   const int my_items = (p.num_items - 1 - int(blockIdx.x)) / int(gridDim.x) + 1;
 
@@ -145,176 +214,201 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
       tma_prefetch_desc(&tm_bias);
-      int g = 0;   // key tiles issued so far (ring position)
-      int qi = 0;  // items that loaded Q so far
+      TileCursor c;
+      cursor_init(p, c, my_items);
+      int issued = 0;
       bool ok = true;
-      for (int i = 0; ok && i < my_items; ++i) {
-        const Item it = decode_item(p, blockIdx.x + i * gridDim.x);
-        if (it.skip) continue;
-        const int nvalid = (it.q0 + kQTile < p.S) ? 2 : 1;
-        const int ib = qi & 1;
-        ok = mbar_wait(bars + (Q_EMPTY + ib) * 8, ((qi >> 1) & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        mbar_expect_tx(bars + (Q_FULL + ib) * 8, nvalid * 8192);
-        for (int w = 0; w < nvalid; ++w)
-          tma_load_4d(base + kSmQ + (ib * 2 + w) * 8192, &tm_q, bars + (Q_FULL + ib) * 8, 0, it.q0 + w * kQTile,
-                      it.h, it.br);
-        ++qi;
-        for (int kt = 0; kt < it.nkt; ++kt, ++g) {
-          const int stage = g % kStages;
-          ok = mbar_wait(bars + (KV_EMPTY + stage) * 8, ((g / kStages) & 1) ^ 1, abort_flag);
+      while (ok && c.valid) {
+        const Item& it = c.it;
+        if (c.kt == 0) {
+          const int ib = c.qi & 1;
+          ok = mbar_wait(bars + (Q_EMPTY + ib) * 8, ((c.qi >> 1) & 1) ^ 1, abort_flag);
           if (!ok) break;
-          const uint32_t full = bars + (KV_FULL + stage) * 8;
-          const uint32_t sbase = base + kSmStage + stage * kStageBytes;
-          mbar_expect_tx(full, 16384 + (it.uniform ? 0 : nvalid * 32768));
-          tma_load_4d(sbase, &tm_k, full, 0, kt * kKTile, it.h, it.br);
-          tma_load_4d(sbase + 8192, &tm_v, full, 0, kt * kKTile, it.h, it.br);
-          if (!it.uniform)
-            for (int w = 0; w < nvalid; ++w)
-              for (int half = 0; half < 2; ++half)
-                tma_load_4d(sbase + 16384 + w * 32768 + half * 16384, &tm_bias, full, kt * kKTile + half * 64,
-                            it.q0 + w * kQTile, it.h, it.b);
+          mbar_expect_tx(bars + (Q_FULL + ib) * 8, it.nvalid * 8192);
+          for (int w = 0; w < it.nvalid; ++w)
+            tma_load_4d(base + kSmQ + (ib * 2 + w) * 8192, &tm_q, bars + (Q_FULL + ib) * 8, 0, it.q0 + w * kQTile,
+                        it.h, it.br);
         }
+        // K + bias of this tile (needed first, by the score MMAs)
+        const int stage = c.g % kStages;
+        ok = mbar_wait(bars + (KB_EMPTY + stage) * 8, ((c.g / kStages) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        const uint32_t full = bars + (KB_FULL + stage) * 8;
+        const uint32_t sbase = base + kSmStage + stage * kStageBytes;
+        mbar_expect_tx(full, 8192 + (it.uniform ? 0 : it.nvalid * 32768));
+        tma_load_4d(sbase, &tm_k, full, 0, c.kt * kKTile, it.h, it.br);
+        if (!it.uniform)
+          for (int w = 0; w < it.nvalid; ++w)
+            for (int half = 0; half < 2; ++half)
+              tma_load_4d(sbase + 8192 + w * 32768 + half * 16384, &tm_bias, full, c.kt * kKTile + half * 64,
+                          it.q0 + w * kQTile, it.h, it.b);
+        // V of this tile
+        const int vs = c.g % kVStages;
+        ok = mbar_wait(bars + (V_EMPTY + vs) * 8, ((c.g / kVStages) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(bars + (V_FULL + vs) * 8, 8192);
+        tma_load_4d(base + kSmV + vs * 8192, &tm_v, bars + (V_FULL + vs) * 8, 0, c.kt * kKTile, it.h, it.br);
+        ++issued;
+        cursor_next(p, c, my_items);
       }
-      if (*abort_flag && g > 0) {
-        const int last = g - 1;
-        mbar_wait(bars + (KV_FULL + last % kStages) * 8, (last / kStages) & 1, abort_flag + 1);
+      // If the loop was abandoned, give copies still in flight a bounded chance to land.
+      if (*abort_flag && issued > 0) {
+        const int last = issued - 1;
+        mbar_wait(bars + (V_FULL + last % kVStages) * 8, (last / kVStages) & 1, abort_flag + 1);
       }
     }
   } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ score MMA issuer (S = Q·Kᵀ + I·Bias)
+    // Runs one key tile ahead of the softmax (also across work items): the only thing it waits for besides
+    // the loads is that a half's S buffer has been read out.
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_bf16(kQTile, kKTile);
-      const uint32_t idesc_o = make_idesc_bf16(kQTile, kHeadDim, false, true);
-      int g = 0, qi = 0;
-      int cs[2] = {0, 0};  // S tiles issued per half
-      int cp[2] = {0, 0};  // P tiles consumed per half
+      constexpr uint32_t idesc_s = make_idesc_bf16(kQTile, kKTile);                // Q·Kᵀ: both operands K-major
+      constexpr uint32_t idesc_b1 = make_idesc_bf16(kQTile, 128, false, true);     // I·Bias, one half: B MN-major
+      constexpr uint32_t idesc_b2 = make_idesc_bf16(kQTile, 256, false, true);     // I·[Bias0|Bias1], both halves
+      const uint32_t ti = tmem_base + kTmemI;
+      const uint32_t d0 = tmem_base + kTmemS;  // S of half 0; half 1 follows 128 columns later
+      int n0 = 0, n1 = 0;                      // S tiles issued per half (phase of S_FREE)
       bool ok = true;
-      auto issue_s = [&](int w, int ib, int stage) -> bool {
-        // S buffer of half w must have been read out by its warpgroup
-        if (!mbar_wait(bars + (S_FREE + w) * 8, (cs[w] & 1) ^ 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t qa = base + kSmQ + (ib * 2 + w) * 8192;
-        const uint32_t ka = base + kSmStage + stage * kStageBytes;
-#pragma unroll
-        for (int ks = 0; ks < 2; ++ks)
-          umma_ss(tmem_base + kTmemS + w * 128, make_smem_desc(qa + ks * 32, 16, 512, kLayoutSw64),
-                  make_smem_desc(ka + ks * 32, 16, 512, kLayoutSw64), idesc_s, ks > 0 ? 1u : 0u);
-        umma_commit(bars + (S_FULL + w) * 8);
-        ++cs[w];
-        return true;
-      };
-      for (int i = 0; ok && i < my_items; ++i) {
-        const Item it = decode_item(p, blockIdx.x + i * gridDim.x);
-        if (it.skip) continue;
-        const int nvalid = (it.q0 + kQTile < p.S) ? 2 : 1;
-        const int ib = qi & 1;
-        ok = mbar_wait(bars + (Q_FULL + ib) * 8, (qi >> 1) & 1, abort_flag);
-        if (!ok) break;
-        ok = mbar_wait(bars + (KV_FULL + g % kStages) * 8, (g / kStages) & 1, abort_flag);
+      TileCursor c;
+      cursor_init(p, c, my_items);
+      while (ok && c.valid) {
+        const Item& it = c.it;
+        const int ib = c.qi & 1, stage = c.g % kStages;
+        if (c.kt == 0) ok = mbar_wait(bars + (Q_FULL + ib) * 8, (c.qi >> 1) & 1, abort_flag);
+        ok = ok && mbar_wait(bars + (KB_FULL + stage) * 8, (c.g / kStages) & 1, abort_flag);
+        // the S buffers must have been read out by their warpgroups
+        ok = ok && mbar_wait(bars + (S_FREE + 0) * 8, (n0 & 1) ^ 1, abort_flag);
+        if (it.nvalid == 2) ok = ok && mbar_wait(bars + (S_FREE + 1) * 8, (n1 & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        for (int w = 0; ok && w < nvalid; ++w) ok = issue_s(w, ib, g % kStages);
-        for (int kt = 0; ok && kt < it.nkt; ++kt, ++g) {
-          const int stage = g % kStages;
-          const bool more = kt + 1 < it.nkt;
-          if (more) {
-            // next tile's scores as soon as its K landed and the S buffers were drained
-            ok = mbar_wait(bars + (KV_FULL + (g + 1) % kStages) * 8, ((g + 1) / kStages) & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            for (int w = 0; ok && w < nvalid; ++w) ok = issue_s(w, ib, (g + 1) % kStages);
-            if (!ok) break;
-          } else {
-            umma_commit(bars + (Q_EMPTY + ib) * 8);  // every S MMA of this item has been issued
-          }
-          for (int w = 0; w < nvalid; ++w) {
-            ok = mbar_wait(bars + (P_FULL + w) * 8, cp[w] & 1, abort_flag);
-            if (!ok) break;
-            ++cp[w];
-            tc_fence_after();
-            const uint32_t pa = base + kSmStage + stage * kStageBytes + 16384 + w * 32768;
-            const uint32_t va = base + kSmStage + stage * kStageBytes + 8192;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              umma_ss(tmem_base + kTmemO + w * 32,
-                      make_smem_desc(pa + (j >> 2) * 16384 + (j & 3) * 32, 16, 1024, kLayoutSw128),
-                      make_smem_desc(va + j * 1024, 16, 512, kLayoutSw64), idesc_o, (kt > 0 || j > 0) ? 1u : 0u);
-            umma_commit(bars + (O_FULL + w) * 8);
-          }
-          if (!ok) break;
-          umma_commit(bars + (KV_EMPTY + stage) * 8);
+        // One descriptor per operand tile; the K steps only add a constant to its address field (in 16-byte
+        // units), which keeps this single-thread issue path down to a few instructions per MMA.
+        const uint32_t sbase = base + kSmStage + stage * kStageBytes;
+        const uint64_t dk = make_smem_desc(sbase, 16, 512, kLayoutSw64);
+        const uint64_t dq0 = make_smem_desc(base + kSmQ + ib * 16384, 16, 512, kLayoutSw64);
+        umma_ss(d0, dq0, dk, idesc_s, 0u);
+        umma_ss(d0, dq0 + 2, dk + 2, idesc_s, 1u);  // second 16 channels: +32 bytes
+        if (it.nvalid == 2) {
+          umma_ss(d0 + 128, dq0 + 512, dk, idesc_s, 0u);  // Q of half 1 lies 8 KiB further
+          umma_ss(d0 + 128, dq0 + 514, dk + 2, idesc_s, 1u);
         }
-        ++qi;
+        if (!it.uniform) {
+          // Bias tiles: [128 query rows][64 keys] blocks with 128-byte swizzle, 16 KiB apart: keys 0-63 and
+          // 64-127 of half 0, then of half 1.  As B[key][query] this is MN-major with 16 query rows (2 KiB)
+          // per K step, so one N=256 MMA chain adds the bias of both halves (their S buffers are adjacent).
+          const uint64_t db = make_smem_desc(sbase + 8192, 16384, 1024, kLayoutSw128);
+          if (it.nvalid == 2) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) umma_ts(d0, ti + j * 8, db + j * 128, idesc_b2, 1u);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) umma_ts(d0, ti + j * 8, db + j * 128, idesc_b1, 1u);
+          }
+        }
+        umma_commit(bars + (S_FULL + 0) * 8);
+        ++n0;
+        if (it.nvalid == 2) {
+          umma_commit(bars + (S_FULL + 1) * 8);
+          ++n1;
+        }
+        umma_commit(bars + (KB_EMPTY + stage) * 8);                      // K and bias are free once these MMAs ran
+        if (c.kt == it.nkt - 1) umma_commit(bars + (Q_EMPTY + ib) * 8);  // last use of this item's Q
+        cursor_next(p, c, my_items);
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ P·V MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_o = make_idesc_bf16(kQTile, kHeadDim, false, true);  // P·V: B is MN-major
+      int n0 = 0, n1 = 0;  // P tiles consumed per half
+      bool ok = true;
+      TileCursor c;
+      cursor_init(p, c, my_items);
+      while (ok && c.valid) {
+        const Item& it = c.it;
+        const int vs = c.g % kVStages;
+        ok = mbar_wait(bars + (V_FULL + vs) * 8, (c.g / kVStages) & 1, abort_flag);
+        const uint64_t dv = make_smem_desc(base + kSmV + vs * 8192, 16, 512, kLayoutSw64);
+        const uint32_t acc0 = c.kt > 0 ? 1u : 0u;
+        ok = ok && mbar_wait(bars + (P_FULL + 0) * 8, n0 & 1, abort_flag);
+        if (!ok) break;
+        ++n0;
+        tc_fence_after();
+        {
+          const uint32_t d = tmem_base + kTmemO, tp = tmem_base + kTmemP;
+          umma_ts(d, tp, dv, idesc_o, acc0);
+#pragma unroll
+          for (int j = 1; j < 8; ++j) umma_ts(d, tp + j * 8, dv + j * 64, idesc_o, 1u);  // 16 keys = 1 KiB per step
+          umma_commit(bars + (O_FULL + 0) * 8);
+        }
+        if (it.nvalid == 2) {
+          ok = mbar_wait(bars + (P_FULL + 1) * 8, n1 & 1, abort_flag);
+          if (!ok) break;
+          ++n1;
+          tc_fence_after();
+          const uint32_t d = tmem_base + kTmemO + 32, tp = tmem_base + kTmemP + 64;
+          umma_ts(d, tp, dv, idesc_o, acc0);
+#pragma unroll
+          for (int j = 1; j < 8; ++j) umma_ts(d, tp + j * 8, dv + j * 64, idesc_o, 1u);
+          umma_commit(bars + (O_FULL + 1) * 8);
+        }
+        umma_commit(bars + (V_EMPTY + vs) * 8);
+        cursor_next(p, c, my_items);
       }
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ softmax warpgroups
     asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-    const int w = warp >> 2;                 // which 128-query half
-    const int m = (warp & 3) * 32 + lane;    // query row inside the half == TMEM lane
+    const int w = warp >> 2;               // which 128-query half
+    const int m = (warp & 3) * 32 + lane;  // query row inside the half == TMEM lane
     const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
-    int g = 0;   // ring position (all tiles of all items, same count as the producer)
+    const uint32_t s_addr = lane_taddr + kTmemS + w * 128;
+    const uint32_t o_addr = lane_taddr + kTmemO + w * 32;
+    const uint32_t p_addr = lane_taddr + kTmemP + w * 64;
+    const float c = p.scale_log2;                 // raw score -> log2-domain logit
+    const float raw_threshold = kRescaleThreshold / c;
+    const uint64_t c2 = pack_f32x2(c, c);
     int ct = 0;  // tiles this half has processed (phase of S_FULL / O_FULL)
     bool ok = true;
     for (int i = 0; ok && i < my_items; ++i) {
       const Item it = decode_item(p, blockIdx.x + i * gridDim.x);
       const int q = it.q0 + w * kQTile + m;  // query position
-      const bool half_valid = it.q0 + w * kQTile < p.S;
       __nv_bfloat16* out_row = p.out + it.br * p.o_br + (long long)q * p.o_s + it.h * p.o_h;
       if (it.skip) {
         if (q < p.S) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0, 0, 0, 0);
+          for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(out_row)[j] = make_uint4(0, 0, 0, 0);
           if (p.lse) p.lse[((long long)it.br * p.S + q) * kHeads + it.h] = -INFINITY;
         }
         continue;
       }
-      if (!half_valid) {
-        g += it.nkt;
-        continue;
-      }
-      float row_max = -INFINITY, row_sum = 0.f;
+      if (w >= it.nvalid) continue;  // this half holds no query of the item
+      float row_max = -INFINITY, row_sum = 0.f;  // row_max in raw score units
+      uint4 gv[4];                               // gate row, fetched during the last key tile
+#pragma unroll
+      for (int j = 0; j < 4; ++j) gv[j] = make_uint4(0, 0, 0, 0);
 
-      for (int kt = 0; kt < it.nkt; ++kt, ++g, ++ct) {
-        const int stage = g % kStages;
-        const uint32_t btile = base + kSmStage + stage * kStageBytes + 16384 + w * 32768;
-        ok = mbar_wait(bars + (KV_FULL + stage) * 8, (g / kStages) & 1, abort_flag);
-        if (!ok) break;
+      for (int kt = 0; kt < it.nkt; ++kt, ++ct) {
+        if (kt == it.nkt - 1 && p.gate != nullptr && q < p.S) {
+          const uint4* gp = reinterpret_cast<const uint4*>(p.gate + it.br * p.g_br + it.h * p.g_h + (long long)q * p.g_s);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) gv[j] = __ldg(gp + j);
+        }
         ok = mbar_wait(bars + (S_FULL + w) * 8, ct & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        float s2[128];  // raw scores, turned into scaled+biased logits in place
-        const uint32_t s_addr = lane_taddr + kTmemS + w * 128;
-        // Quarter by quarter (32 keys): TMEM load, the matching 64 bytes of bias, then the
-        // scale+bias FMA; keeps only one quarter of bias words in flight.
-#define B200TA_SCORE_QUARTER(QI)                                                                       \
-  {                                                                                                    \
-    tmem_ld32_f128<QI * 32>(s_addr + QI * 32, s2);                                                     \
-    uint4 bv[4];                                                                                       \
-    _Pragma("unroll") for (int c = 0; c < 4; ++c) bv[c] =                                              \
-        lds128(btile + (QI >> 1) * 16384 + sw128_offset(m, (QI & 1) * 4 + c));                         \
-    tmem_ld_wait();                                                                                    \
-    _Pragma("unroll") for (int c = 0; c < 4; ++c) {                                                    \
-      const uint32_t bw[4] = {bv[c].x, bv[c].y, bv[c].z, bv[c].w};                                     \
-      _Pragma("unroll") for (int e = 0; e < 4; ++e) {                                                  \
-        const int j0 = QI * 32 + c * 8 + 2 * e;                                                        \
-        s2[j0] = fmaf(s2[j0], p.scale_log2, bf16_lo(bw[e]));                                           \
-        s2[j0 + 1] = fmaf(s2[j0 + 1], p.scale_log2, bf16_hi(bw[e]));                                   \
-      }                                                                                                \
-    }                                                                                                  \
-  }
-        B200TA_SCORE_QUARTER(0)
-        B200TA_SCORE_QUARTER(1)
-        B200TA_SCORE_QUARTER(2)
-        B200TA_SCORE_QUARTER(3)
-#undef B200TA_SCORE_QUARTER
+        float s2[128];  // raw scores (bias included) of this row against the tile's 128 keys
+        tmem_ld32_f128<0>(s_addr, s2);
+        tmem_ld32_f128<32>(s_addr + 32, s2);
+        tmem_ld32_f128<64>(s_addr + 64, s2);
+        tmem_ld32_f128<96>(s_addr + 96, s2);
+        tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bars + (S_FREE + w) * 8);
+        if (lane == 0) mbar_arrive(bars + (S_FREE + w) * 8);  // the S buffer can take the next tile's scores
 
         if (it.uniform) {
-          // no valid key, eager semantics: every logit is the same (the bias tile was not loaded)
+          // no valid key, eager semantics: every logit is the same
 #pragma unroll
           for (int j = 0; j < 128; ++j) s2[j] = 0.f;
         }
@@ -324,49 +418,58 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           for (int j = 0; j < 128; ++j)
             if (j >= rem) s2[j] = -INFINITY;
         }
-        float tile_max = -INFINITY;
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
 #pragma unroll
-        for (int j = 0; j < 128; ++j) tile_max = fmaxf(tile_max, s2[j]);
-        // Lazy running max: the reference point of the exponentials only moves when the
-        // true max has grown by more than 2^8, so most tiles need no rescale of O.
+        for (int j = 0; j < 64; ++j) mx[j & 3] = max3_f32(mx[j & 3], s2[2 * j], s2[2 * j + 1]);
+        const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        // Lazy running max: the reference point of the exponentials only moves when the true max has
+        // grown by more than 2^8, so most tiles need no rescale of O.
         float alpha = 1.f;
         if (kt == 0) {
           row_max = tile_max;
-        } else if (tile_max > row_max + 8.f) {
-          alpha = ex2_approx(row_max - tile_max);
+        } else if (tile_max > row_max + raw_threshold) {
+          alpha = ex2_approx((row_max - tile_max) * c);
           row_max = tile_max;
         }
-        float tile_sum = 0.f;
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          uint32_t pk[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float p0 = ex2_approx(s2[c * 8 + 2 * e] - row_max);
-            const float p1 = ex2_approx(s2[c * 8 + 2 * e + 1] - row_max);
-            tile_sum += p0 + p1;
-            pk[e] = pack_bf16x2(p0, p1);
-          }
-          sts128(btile + (c >> 3) * 16384 + sw128_offset(m, c & 7), make_uint4(pk[0], pk[1], pk[2], pk[3]));
-        }
-        row_sum = fmaf(row_sum, alpha, tile_sum);
         if (kt > 0) {
-          // the previous tile's P·V must have landed in O before O is rescaled or added to
+          // the previous tile's P·V must be complete before P is overwritten and O rescaled
           ok = mbar_wait(bars + (O_FULL + w) * 8, (ct - 1) & 1, abort_flag);
           if (!ok) break;
+          tc_fence_after();
           if (__any_sync(0xffffffffu, alpha != 1.f)) {
-            tc_fence_after();
             uint32_t t[32];
-            tmem_ld32(lane_taddr + kTmemO + w * 32, t);
+            tmem_ld32(o_addr, t);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) t[j] = __float_as_uint(__uint_as_float(t[j]) * alpha);
-            tmem_st32(lane_taddr + kTmemO + w * 32, t);
-            tmem_st_wait();
-            tc_fence_before();
+            tmem_st32(o_addr, t);
           }
         }
-        fence_proxy_async_smem();
+        // p = 2^(c * (s - row_max)); bf16 pairs go back to TMEM as the A operand of P·V
+        const float nmc = -row_max * c;
+        const uint64_t nmc2 = pack_f32x2(nmc, nmc);
+        uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};  // four independent packed partial sums
+#pragma unroll
+        for (int qtr = 0; qtr < 4; ++qtr) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int j0 = qtr * 32 + 2 * e;
+            float d0, d1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(s2[j0], s2[j0 + 1]), c2, nmc2), d0, d1);
+            const float p0 = ex2_approx(d0), p1 = ex2_approx(d1);
+            sum2[e & 3] = add_f32x2(sum2[e & 3], pack_f32x2(p0, p1));
+            pk[e] = pack_bf16x2(p0, p1);
+          }
+          tmem_st16(p_addr + qtr * 16, pk);
+        }
+        {
+          float a0, a1;
+          unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), a0, a1);
+          row_sum = fmaf(row_sum, alpha, a0 + a1);
+        }
+        tmem_st_wait();
+        tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + (P_FULL + w) * 8);
       }
@@ -378,7 +481,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       float o[32];
       {
         uint32_t t[32];
-        tmem_ld32(lane_taddr + kTmemO + w * 32, t);
+        tmem_ld32(o_addr, t);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(t[j]);
@@ -388,17 +491,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const float inv = 1.f / row_sum;
         uint32_t pk[16];
         if (p.gate != nullptr) {
-          const uint4* gp = reinterpret_cast<const uint4*>(p.gate + it.br * p.g_br + it.h * p.g_h + (long long)q * p.g_s);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const uint4 gv = __ldg(gp + c);
-            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t gw[4] = {gv[j].x, gv[j].y, gv[j].z, gv[j].w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              // sigmoid(x) = 1 / (1 + 2^(-x*log2e))
-              const float s0 = rcp_approx(1.f + ex2_approx(-1.4426950408889634f * bf16_lo(gw[e])));
-              const float s1 = rcp_approx(1.f + ex2_approx(-1.4426950408889634f * bf16_hi(gw[e])));
-              pk[c * 4 + e] = pack_bf16x2(o[c * 8 + 2 * e] * inv * s0, o[c * 8 + 2 * e + 1] * inv * s1);
+              // sigmoid(x) = 0.5 * tanh(x / 2) + 0.5
+              const float s0 = fmaf(0.5f, tanh_approx(0.5f * bf16_lo(gw[e])), 0.5f);
+              const float s1 = fmaf(0.5f, tanh_approx(0.5f * bf16_hi(gw[e])), 0.5f);
+              pk[j * 4 + e] = pack_bf16x2(o[j * 8 + 2 * e] * inv * s0, o[j * 8 + 2 * e + 1] * inv * s1);
             }
           }
         } else {
@@ -406,11 +507,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(o[2 * j] * inv, o[2 * j + 1] * inv);
         }
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-          reinterpret_cast<uint4*>(out_row)[c] = make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+        for (int j = 0; j < 4; ++j)
+          reinterpret_cast<uint4*>(out_row)[j] = make_uint4(pk[j * 4], pk[j * 4 + 1], pk[j * 4 + 2], pk[j * 4 + 3]);
         if (p.lse)
           p.lse[((long long)it.br * p.S + q) * kHeads + it.h] =
-              it.uniform ? -INFINITY : 0.6931471805599453f * (row_max + __log2f(row_sum));
+              it.uniform ? -INFINITY : 0.6931471805599453f * (row_max * c + __log2f(row_sum));
       }
     }
   }
@@ -439,6 +540,7 @@ int b200ta_attention(const void* q, const void* k, const void* v, const void* ga
   B200TA_REQUIRE(q && k && v && bias && out, "attention: NULL pointer");
   B200TA_REQUIRE(B > 0 && R > 0 && S > 0, "attention: bad sizes B=%d R=%d S=%d", B, R, S);
   B200TA_REQUIRE(S_pad >= S && S_pad % 8 == 0, "attention: S_pad=%d must be a multiple of 8 and >= S=%d", S_pad, S);
+  B200TA_REQUIRE(softmax_scale > 0.f, "attention: softmax_scale must be positive");
   B200TA_REQUIRE(s_br % 8 == 0 && s_h % 8 == 0 && s_s % 8 == 0 && s_s > 0, "attention: q/k/v strides must be multiples of 8 elements");
   B200TA_REQUIRE(bs_b % 8 == 0 && bs_h % 8 == 0 && bs_q % 8 == 0 && bs_q > 0, "attention: bias strides must be multiples of 8 elements");
   B200TA_REQUIRE(os_br % 8 == 0 && os_s % 8 == 0 && os_h % 8 == 0, "attention: out strides must be multiples of 8 elements");

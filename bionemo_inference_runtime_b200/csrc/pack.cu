@@ -95,10 +95,11 @@ int b200ta_pack_node_weights(const void* ln_w, const void* ln_b, const void* w_i
   if (rc != B200TA_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   char* base = static_cast<char*>(packed);
-  constexpr float kLog2e = 1.4426950408889634f;
+  // the attention kernel adds the bias to q·k before the softmax scale: store bias / scale = bias * sqrt(head_dim)
+  constexpr float kBiasScale = 5.656854249492381f;
   fold_rows_kernel<<<kNodeRows, kC, 0, s>>>(
       w_in, 4 * kHeads * kHeadDim, w_bias, kHeads, b_in, ln_w, ln_b, weight_dtype, 4 * kHeads * kHeadDim,
-      4 * kHeads * kHeadDim + kHeads, kLog2e, reinterpret_cast<__nv_bfloat16*>(base + kNodeWOff),
+      4 * kHeads * kHeadDim + kHeads, kBiasScale, reinterpret_cast<__nv_bfloat16*>(base + kNodeWOff),
       reinterpret_cast<float2*>(base + kNodeScOff), reinterpret_cast<int*>(base + kNodeFlagsOff));
   convert_kernel<<<(kC * kC + 255) / 256, 256, 0, s>>>(w_out, weight_dtype, size_t(kC) * kC,
                                                        reinterpret_cast<__nv_bfloat16*>(base + kNodeWoOff), nullptr);

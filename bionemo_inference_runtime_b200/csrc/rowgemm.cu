@@ -160,13 +160,13 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           const int n = MODE == kEpilogue ? 128 : (u < 2 ? 256 : 16);
           const uint32_t idesc = make_idesc_bf16(kTileM, n);
           const uint32_t d = tmem_base + slot * kSlotCols;
+          // one descriptor per operand; each K step adds a constant to the address field (16-byte units)
+          const uint64_t da = make_smem_desc(base + L::kA + stage * 32768, 16, 1024, kLayoutSw128);
+          const uint64_t db = make_smem_desc(base + L::kW + u * 256 * 128, 16, 1024, kLayoutSw128);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t a_addr = base + L::kA + stage * 32768 + (k >> 2) * 16384 + (k & 3) * 32;
-            const uint32_t b_addr = base + L::kW + (k >> 2) * L::kWHalf + u * 256 * 128 + (k & 3) * 32;
-            umma_ss(d, make_smem_desc(a_addr, 16, 1024, kLayoutSw128),
-                    make_smem_desc(b_addr, 16, 1024, kLayoutSw128), idesc, k > 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < 8; ++k)
+            umma_ss(d, da + ((k >> 2) * (16384 >> 4) + (k & 3) * 2), db + ((k >> 2) * (L::kWHalf >> 4) + (k & 3) * 2),
+                    idesc, k > 0 ? 1u : 0u);
           umma_commit(bars + (ACC_FULL + slot) * 8);
         }
         if (!ok) break;

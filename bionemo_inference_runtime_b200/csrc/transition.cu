@@ -152,12 +152,14 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                  mbar_wait(bars + (ACC1_FREE + e) * 8, par ^ 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
+            // one descriptor per operand; each K step adds a constant to the address field (16-byte units)
+            const uint64_t da = make_smem_desc(base + kSmX + xs * 32768, 16, 1024, kLayoutSw128);
+            const uint64_t db = make_smem_desc(base + kSmW1 + e * 32768, 16, 1024, kLayoutSw128);
+            const uint32_t d1 = tmem_base + kTmemAcc1 + e * 128;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-              const uint32_t a = base + kSmX + xs * 32768 + (k >> 2) * 16384 + (k & 3) * 32;
-              const uint32_t b = base + kSmW1 + e * 32768 + (k >> 2) * 16384 + (k & 3) * 32;
-              umma_ss(tmem_base + kTmemAcc1 + e * 128, make_smem_desc(a, 16, 1024, kLayoutSw128),
-                      make_smem_desc(b, 16, 1024, kLayoutSw128), idesc, k > 0 ? 1u : 0u);
+              const uint32_t off = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
+              umma_ss(d1, da + off, db + off, idesc, k > 0 ? 1u : 0u);
             }
             umma_commit(bars + (ACC1_FULL + e) * 8);
             umma_commit(bars + (W1_EMPTY + e) * 8);
@@ -173,13 +175,12 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (ok && jj == 0) ok = mbar_wait(bars + (ACC2_FREE + (i & 1)) * 8, ((i >> 1) & 1) ^ 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
+            const uint64_t dh = make_smem_desc(base + kSmH + e * 16384, 16, 1024, kLayoutSw128);
+            const uint64_t dw = make_smem_desc(base + kSmW2 + e * 16384, 16, 1024, kLayoutSw128);
+            const uint32_t d2 = tmem_base + kTmemAcc2 + (i & 1) * 128;
+            umma_ss(d2, dh, dw, idesc, jj > 0 ? 1u : 0u);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint32_t a = base + kSmH + e * 16384 + k * 32;
-              const uint32_t b = base + kSmW2 + e * 16384 + k * 32;
-              umma_ss(tmem_base + kTmemAcc2 + (i & 1) * 128, make_smem_desc(a, 16, 1024, kLayoutSw128),
-                      make_smem_desc(b, 16, 1024, kLayoutSw128), idesc, (jj > 0 || k > 0) ? 1u : 0u);
-            }
+            for (int k = 1; k < 4; ++k) umma_ss(d2, dh + k * 2, dw + k * 2, idesc, 1u);
             umma_commit(bars + (W2_EMPTY + e) * 8);
             umma_commit(bars + (H_FREE + e) * 8);
             if (jj == kChunks - 1) umma_commit(bars + (ACC2_FULL + (i & 1)) * 8);

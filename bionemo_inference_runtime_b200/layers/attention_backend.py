@@ -132,7 +132,7 @@ class B200TriangleAttention(AttentionBackend):
         else:
             if tri_bias.shape[-1] % 8 != 0:
                 tri_bias = torch.nn.functional.pad(tri_bias, (0, -tri_bias.shape[-1] % 8))
-            bias2 = (tri_bias.float() * ops.LOG2E).to(torch.bfloat16).contiguous()  # kernel wants log2 units
+            bias2 = (tri_bias.float() * ops.BIAS_SCALE).to(torch.bfloat16).contiguous()  # kernel wants bias / scale
         if output is None:
             output = torch.empty((B * I, J, ops.HEADS, ops.HEAD_DIM), dtype=torch.bfloat16, device=q.device)
         o4 = output.view(B * I, J, ops.HEADS, ops.HEAD_DIM)

@@ -115,7 +115,7 @@ class TriangleAttention(nn.Module):
         else:
             pad = -triangle_bias.shape[-1] % 8
             tb = torch.nn.functional.pad(triangle_bias, (0, pad)) if pad else triangle_bias
-            bias2 = (tb.float() * ops.LOG2E).to(torch.bfloat16).contiguous()
+            bias2 = (tb.float() * ops.BIAS_SCALE).to(torch.bfloat16).contiguous()
         out = residual if (residual is not None and inplace_residual) else None
         if out is None:
             out = torch.empty((B, R, S, ops.C), dtype=torch.bfloat16, device=x.device)

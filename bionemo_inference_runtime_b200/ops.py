@@ -18,7 +18,7 @@ C = 128
 HEADS = 4
 HEAD_DIM = 32
 HIDDEN = 512
-LOG2E = 1.4426950408889634
+BIAS_SCALE = 5.656854249492381  # sqrt(head_dim): the kernels keep the triangle bias divided by the softmax scale
 
 
 def _stream() -> int:

@@ -201,7 +201,7 @@ def test_empty_rows_zeros_mode_and_lengths_beyond_every_boundary():
     for mode, name in ((_lib.EMPTY_ROW_ZEROS, "zeros"), (_lib.EMPTY_ROW_UNIFORM, "uniform")):
         want, want_lse = orc.attention_core(q, k, v, bias[..., :S].float(), lens, 1 / math.sqrt(32), empty_rows=name)
         lse = torch.full((B * R, S, 4), float("nan"), device=DEV)
-        bias_dev = (bias.float() * ops.LOG2E).bfloat16().to(DEV)
+        bias_dev = (bias.float() * ops.BIAS_SCALE).bfloat16().to(DEV)
         out = ops.attention(qkvg.to(DEV), bias_dev, lens.to(DEV), B, R, S, gate=False, lse=lse, empty_row_mode=mode)
         torch.testing.assert_close(out.float().cpu().view(B * R, S, 4, 32), want, rtol=2e-2, atol=3e-2)
         valid = lens > 0
