@@ -52,6 +52,12 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
          c_int64, c_int64, c_int, c_int, c_int, c_void_p],
     ),
+    "b200ta_node_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "b200ta_node_forward": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p,
+         c_int64, c_int64, c_int64, c_void_p, c_size_t, c_int, c_int, c_void_p],
+    ),
     "b200ta_transition": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p],

@@ -19,7 +19,7 @@ CSRC = Path(__file__).resolve().parent
 PKG = CSRC.parent
 LIB = PKG / "libb200ta.so"
 OBJ_DIR = CSRC / "build"
-SOURCES = ["host.cu", "pack.cu", "rowgemm.cu", "attention.cu", "transition.cu", "simt.cu"]
+SOURCES = ["host.cu", "pack.cu", "rowgemm.cu", "attention.cu", "node.cu", "transition.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--use_fast_math",

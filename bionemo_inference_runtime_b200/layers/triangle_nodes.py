@@ -239,6 +239,11 @@ class TriangleAttentionNode(nn.Module):
 
         policy = self.mha.chunk_policy
         chunked = policy is not None and policy.should_chunk(xk) and policy.chunk_size < R
+        if not chunked and not self.transposed_bias:
+            # common case: one library call for the whole node, intermediates in one workspace
+            ws = ensure_buffer(buffers, "tri_attn_workspace", (ops.node_workspace_bytes(B, N),), torch.uint8, x.device)
+            return ops.node_forward(x, packed, lengths, eps, ending=ending, residual=residual, out=out, workspace=ws,
+                                    empty_row_mode=mode)
         bias = ensure_buffer(buffers, "tri_attn_bias", (B, ops.HEADS, S, ops.pad8(S)), torch.bfloat16, x.device)
         if self.transposed_bias and bias is None:
             bias = torch.zeros((B, ops.HEADS, S, ops.pad8(S)), dtype=torch.bfloat16, device=x.device)

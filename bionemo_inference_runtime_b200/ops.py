@@ -158,6 +158,47 @@ def attention(qkvg: torch.Tensor, bias: torch.Tensor, lengths: torch.Tensor | No
     return out
 
 
+def node_workspace_bytes(B: int, N: int) -> int:
+    return int(_lib.load().b200ta_node_workspace_bytes(B, N))
+
+
+def node_forward(z: torch.Tensor, packed: torch.Tensor, lengths: torch.Tensor | None, eps: float = 1e-5, *,
+                 ending: bool = False, residual: bool = False, out: torch.Tensor | None = None,
+                 workspace: torch.Tensor | None = None, empty_row_mode: int = _lib.EMPTY_ROW_UNIFORM) -> torch.Tensor:
+    """A whole triangle-attention node in one library call (``b200ta_node_forward``).
+
+    ``z`` / ``out`` are square pair tensors ``[B, N, N, 128]`` in the caller's order; ``lengths`` is ``[B, N]`` int32
+    (valid keys per kernel row, i.e. per second pair index for the ending node) or ``None``; ``workspace`` is a
+    uint8 scratch tensor of at least :func:`node_workspace_bytes` bytes (allocated when omitted).
+    """
+    _require_cuda_bf16("z", z)
+    B, R, S, sb, sr, ss = _pair_strides(z, ending)
+    if R != S:
+        raise ValueError("node_forward needs a square pair tensor")
+    if out is None:
+        out = torch.empty((B, R, S, C), dtype=torch.bfloat16, device=z.device)
+    _require_cuda_bf16("out", out)
+    oB, oR, oS, osb, osr, oss = _pair_strides(out, ending)
+    if (oB, oR, oS) != (B, R, S):
+        raise ValueError(f"out shape {tuple(out.shape)} does not match z {tuple(z.shape)}")
+    need = node_workspace_bytes(B, R)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=z.device)
+    elif workspace.numel() * workspace.element_size() < need or not workspace.is_contiguous():
+        raise ValueError(f"workspace must be contiguous and hold at least {need} bytes")
+    if lengths is not None:
+        if lengths.dtype != torch.int32 or not lengths.is_cuda or lengths.numel() != B * R:
+            raise ValueError(f"lengths must be a CUDA int32 tensor with B*N={B * R} values")
+        lengths = lengths.reshape(B, R)
+        ls = (lengths.stride(0), lengths.stride(1))
+    else:
+        ls = (0, 0)
+    _lib.call("b200ta_node_forward", z.data_ptr(), sb, sr, ss, packed.data_ptr(), float(eps), _ptr(lengths), *ls,
+              int(empty_row_mode), 1 if residual else 0, out.data_ptr(), osb, osr, oss, workspace.data_ptr(),
+              workspace.numel() * workspace.element_size(), B, R, _stream())
+    return out
+
+
 def epilogue(og: torch.Tensor, packed: torch.Tensor, residual: torch.Tensor | None, out: torch.Tensor | None = None,
              *, ending: bool = False) -> torch.Tensor:
     """``out = residual + og · W_oᵀ + b_o``.

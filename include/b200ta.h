@@ -103,7 +103,8 @@ int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const voi
  *   z          [B,R,S,128] via element strides (zs_b, zs_r, zs_s); channel stride 1.
  *   qkvg       output, four planes (q,k,v,g) of [B*R, 4 heads, S, 32]:
  *              element (which, br, h, s, d) at which*qs_which + br*qs_br + h*qs_h + s*qs_s + d.
- *   bias       output, bias[b,h,q=r,k=s] * log2(e) at b*bs_b + h*bs_h + r*bs_q + s*bs_k;
+ *   bias       output, bias[b,h,q=r,k=s] * sqrt(32) (i.e. divided by the softmax scale, the form
+ *              b200ta_attention consumes) at b*bs_b + h*bs_h + r*bs_q + s*bs_k;
  *              entries S <= s < S_pad are written as zero.  May be NULL (no bias written).
  *   want_qkvg  0 = bias only (used to finish the bias of all rows before a
  *              row-chunked pass), 1 = both.
@@ -118,13 +119,13 @@ int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
 
 /*
  * Attention core.  For every (b, r, h) and query s:
- *   o[s,:] = softmax_t( scale * q[s]·k[t] + bias[b,h,s,t] ; t < len[b,r] ) · v[t,:]
+ *   o[s,:] = softmax_t( scale * (q[s]·k[t] + bias[b,h,s,t]) ; t < len[b,r] ) · v[t,:]
  * optionally multiplied by sigmoid(gate) in the epilogue.
  *
  *   q,k,v,gate [B*R, 4, S, 32] via element strides (br, h, s); d stride 1; gate may be NULL.
- *   bias       [B, 4, S, S_pad] with log2(e) already folded in (as b200ta_prologue
- *              writes it) when bias_is_log2 != 0, plain otherwise... (bias_is_log2 must be 1
- *              in this version); element strides (b, h, q); key stride 1; S_pad % 8 == 0.
+ *   bias       [B, 4, S, S_pad]: the additive triangle bias DIVIDED by softmax_scale (the tensor core adds
+ *              it to q·k before the scale is applied; b200ta_prologue writes it in this form);
+ *              element strides (b, h, q); key stride 1; S_pad % 8 == 0.
  *   lengths    int32, len[b,r] at b*ls_b + r*ls_r (ls_r = 0 broadcasts one length per item).
  *              NULL = every key valid.
  *   out        [B*R, S, 4, 32] via element strides (br, s, h); d stride 1.
@@ -154,6 +155,24 @@ int b200ta_attention(const void* q, const void* k, const void* v, const void* ga
 int b200ta_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, const void* packed,
                     const void* residual, int64_t rs_b, int64_t rs_r, int64_t rs_s, void* out,
                     int64_t os_b, int64_t os_r, int64_t os_s, int B, int R, int S, void* stream);
+
+/*
+ * Whole node in one call: prologue -> attention -> epilogue on `stream`, intermediates in `workspace`
+ * (b200ta_node_workspace_bytes(B, N) bytes, 256-byte aligned, caller-owned; contents are scratch).
+ *
+ *   z, out     square pair tensors [B,N,N,128] via element strides in kernel order (b, row, sequence): the
+ *              starting node passes (stride_b, stride_i, stride_j), the ending node (stride_b, stride_j, stride_i).
+ *   lengths    int32 valid-key count per (b, row) at b*ls_b + row*ls_r, or NULL (all keys valid).
+ *   add_residual  1: out = z + update (out may alias z), 0: out = update.
+ *
+ * Replaces: TriangleAttentionNode.forward (bionemo_ir/_torch/layers/triangle_nodes.py:195-250) below the
+ * Python layer, i.e. what a single native call per node would bind.
+ */
+size_t b200ta_node_workspace_bytes(int B, int N);
+int b200ta_node_forward(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, const void* packed, float eps,
+                        const int32_t* lengths, int64_t ls_b, int64_t ls_r, int empty_row_mode,
+                        int add_residual, void* out, int64_t os_b, int64_t os_r, int64_t os_s,
+                        void* workspace, size_t workspace_bytes, int B, int N, void* stream);
 
 /* ---- pair transition ---------------------------------------------------------------
  *

@@ -184,8 +184,30 @@ def test_inplace_residual_buffers_and_no_mask():
     zc = z.clone()
     got = node(zc, buffers=bufs, residual=True, inplace_residual=True)
     assert got is zc and torch.equal(zc, want)
-    assert {"tri_attn_output", "tri_attn_qkvg", "tri_attn_bias"} <= set(bufs)
+    assert "tri_attn_workspace" in bufs
     assert torch.equal(node(z, buffers=bufs, residual=True), want)  # buffers reused
+    chunky = build_node(w, orc.STARTING, chunk_policy=b200.ChunkPolicy(chunk_size=40, min_size=1))
+    cb: dict = {}
+    assert torch.equal(chunky(z, buffers=cb, residual=True), want)
+    assert {"tri_attn_output", "tri_attn_qkvg", "tri_attn_bias"} <= set(cb)
+
+
+def test_single_call_node_equals_the_three_stage_calls():
+    torch.manual_seed(14)
+    n = 90
+    w = bf16_weights(orc.make_node_weights(36, identity_ln=False, out_bias=True))
+    packed = ops.pack_node_weights(*[None if t is None else t.bfloat16().to(DEV) for t in
+                                     (w.ln_w, w.ln_b, w.w_in, w.b_in, w.w_bias, w.w_out, w.b_out)])
+    z = torch.randn(2, n, n, 128).bfloat16().to(DEV)
+    lens = torch.randint(0, n + 1, (2, n), dtype=torch.int32, device=DEV)
+    for ending in (False, True):
+        qkvg, bias = ops.prologue(z, packed, ending=ending)
+        og = ops.attention(qkvg, bias, lens, 2, n, n)
+        want = ops.epilogue(og, packed, z, ending=ending)
+        got = ops.node_forward(z, packed, lens, ending=ending, residual=True)
+        assert torch.equal(got, want)
+    with pytest.raises(ValueError, match="workspace"):
+        ops.node_forward(z, packed, lens, workspace=torch.empty(1024, dtype=torch.uint8, device=DEV))
 
 
 def test_empty_rows_zeros_mode_and_lengths_beyond_every_boundary():
