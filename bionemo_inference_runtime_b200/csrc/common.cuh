@@ -36,13 +36,12 @@ int fail(int code, const char* fmt, ...);
     if (!(cond)) return ::b200ta::fail(B200TA_ERR_INVALID, __VA_ARGS__);               \
   } while (0)
 
-// Per-device state created on first use (never during stream capture: callers
-// are told to make their first call outside a capture).
+// Per-device state created on first use (a symbol-address lookup and a property query; no allocation).
+// Callers are told to make their first call outside a stream capture.
 struct DeviceState {
   int device = -1;
   int num_sms = 0;
-  int* status_host = nullptr;  // mapped pinned word kernels write on a timed-out wait
-  int* status_dev = nullptr;   // device alias of status_host
+  int* status_dev = nullptr;  // device word kernels write when they abandon a bounded wait
 };
 int get_device_state(DeviceState** out);
 

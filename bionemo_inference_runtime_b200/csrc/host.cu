@@ -20,6 +20,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
+
+// Written by a kernel that abandoned a bounded wait; read back by b200ta_device_status().
+__device__ int g_status_word = 0;
 }  // namespace
 
 int fail(int code, const char* fmt, ...) {
@@ -42,13 +45,11 @@ int get_device_state(DeviceState** out) {
     if (prop.major != 10)
       return fail(B200TA_ERR_UNSUPPORTED, "device %d is sm_%d%d; these kernels are built for sm_100a only",
                   dev, prop.major, prop.minor);
-    int* host = nullptr;
-    B200TA_CHECK_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&host), 64, cudaHostAllocMapped));
-    *host = 0;
+    // The status word is a file-scope device variable (one per device that loads the library), so creating
+    // the state allocates nothing; its address is looked up once, with this device current.
     int* devp = nullptr;
-    B200TA_CHECK_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&devp), host, 0));
+    B200TA_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&devp), g_status_word));
     st.num_sms = prop.multiProcessorCount;
-    st.status_host = host;
     st.status_dev = devp;
     st.device = dev;
   }
@@ -114,7 +115,7 @@ int b200ta_device_status(int* status) {
   b200ta::DeviceState* st = nullptr;
   int rc = b200ta::get_device_state(&st);
   if (rc != B200TA_OK) return rc;
-  *status = *reinterpret_cast<volatile int*>(st->status_host);
+  B200TA_CHECK_CUDA(cudaMemcpy(status, st->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
   return B200TA_OK;
 }
 
@@ -122,7 +123,8 @@ int b200ta_reset_device_status(void) {
   b200ta::DeviceState* st = nullptr;
   int rc = b200ta::get_device_state(&st);
   if (rc != B200TA_OK) return rc;
-  *reinterpret_cast<volatile int*>(st->status_host) = 0;
+  const int zero = 0;
+  B200TA_CHECK_CUDA(cudaMemcpy(st->status_dev, &zero, sizeof(int), cudaMemcpyHostToDevice));
   return B200TA_OK;
 }
 

@@ -12,7 +12,7 @@
  * (which works on the transposed pair tensor) passes the same buffers with the
  * R and S strides swapped instead of materialising a transpose.
  *
- * The first call on a device creates a small per-device state (a mapped status
+ * The first call on a device creates a small per-device state (the address of a status
  * word); make it outside any stream capture.
  *
  * Each declaration cites the interface of the reference runtime it replaces
