@@ -58,6 +58,12 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p,
          c_int64, c_int64, c_int64, c_void_p, c_size_t, c_int, c_int, c_void_p],
     ),
+    "b200ta_node_static_max_positions": (c_int, []),
+    "b200ta_node_forward_static": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p,
+         c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
+    ),
     "b200ta_transition": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p],

@@ -199,6 +199,39 @@ def node_forward(z: torch.Tensor, packed: torch.Tensor, lengths: torch.Tensor | 
     return out
 
 
+def node_static_max_positions() -> int:
+    return int(_lib.load().b200ta_node_static_max_positions())
+
+
+def node_forward_static(z: torch.Tensor, packed: torch.Tensor, lengths: torch.Tensor | None, out: torch.Tensor,
+                        eps: float = 1e-5, *, ending: bool = False, residual: bool = False,
+                        empty_row_mode: int = _lib.EMPTY_ROW_UNIFORM) -> torch.Tensor:
+    """:func:`node_forward` through ``b200ta_node_forward_static``: no workspace, nothing allocated.
+
+    For callers that must not allocate device memory (for example inside a stream capture): the intermediates
+    go to an array built into the library, which limits the problem to ``B*N*N <= node_static_max_positions()``
+    and means that calls which could overlap on the GPU must be ordered by the caller.  ``out`` has to be given
+    (this wrapper allocates nothing either) and may be ``z`` itself when ``residual`` is set.
+    """
+    _require_cuda_bf16("z", z)
+    _require_cuda_bf16("out", out)
+    B, R, S, sb, sr, ss = _pair_strides(z, ending)
+    if R != S:
+        raise ValueError("node_forward_static needs a square pair tensor")
+    oB, oR, oS, osb, osr, oss = _pair_strides(out, ending)
+    if (oB, oR, oS) != (B, R, S):
+        raise ValueError(f"out shape {tuple(out.shape)} does not match z {tuple(z.shape)}")
+    if lengths is not None:
+        if lengths.dtype != torch.int32 or not lengths.is_cuda or lengths.dim() != 2 or tuple(lengths.shape) != (B, R):
+            raise ValueError(f"lengths must be a CUDA int32 tensor of shape [{B}, {R}]")
+        ls = (lengths.stride(0), lengths.stride(1))
+    else:
+        ls = (0, 0)
+    _lib.call("b200ta_node_forward_static", z.data_ptr(), sb, sr, ss, packed.data_ptr(), float(eps), _ptr(lengths), *ls,
+              int(empty_row_mode), 1 if residual else 0, out.data_ptr(), osb, osr, oss, B, R, _stream())
+    return out
+
+
 def epilogue(og: torch.Tensor, packed: torch.Tensor, residual: torch.Tensor | None, out: torch.Tensor | None = None,
              *, ending: bool = False) -> torch.Tensor:
     """``out = residual + og · W_oᵀ + b_o``.

@@ -174,6 +174,29 @@ int b200ta_node_forward(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s,
                         int add_residual, void* out, int64_t os_b, int64_t os_r, int64_t os_s,
                         void* workspace, size_t workspace_bytes, int B, int N, void* stream);
 
+/*
+ * The same node without any workspace argument, for callers that are not allowed to allocate device memory:
+ * code running while a stream is being captured into a CUDA graph (a capture forbids cudaMalloc), request
+ * handlers of a serving process whose own pool already owns all device memory, or a host that pre-sizes
+ * everything at start-up and treats a later allocation as a bug.  The intermediates live in a fixed array that
+ * is part of the library image: about 5.25 MiB of device memory on every GPU that loads the library, held
+ * until the process exits.  This entry point has no counterpart in the reference runtime.
+ *
+ * Limit: B*N*N <= b200ta_node_static_max_positions() (4096 pair positions, e.g. one 64 x 64 pair tensor);
+ * larger problems are refused with B200TA_ERR_UNSUPPORTED and a message, and belong to b200ta_node_forward.
+ * The call makes no cudaMalloc/cudaFree and calls no allocating routine.  Its first call on a device looks up
+ * the array's device address (with that device current); make that first call before starting a stream capture.
+ * Every call uses the one array and leaves its last intermediates there, so two calls that can overlap on the
+ * GPU (different streams, or different host threads without ordering) race on it: order them on one stream
+ * or with events.  Nothing in the array needs clearing between calls: each call writes all it later reads.
+ * Arguments are those of b200ta_node_forward minus the workspace.
+ */
+int b200ta_node_static_max_positions(void);
+int b200ta_node_forward_static(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, const void* packed,
+                               float eps, const int32_t* lengths, int64_t ls_b, int64_t ls_r,
+                               int empty_row_mode, int add_residual, void* out, int64_t os_b, int64_t os_r,
+                               int64_t os_s, int B, int N, void* stream);
+
 /* ---- pair transition ---------------------------------------------------------------
  *
  * out = [x +] mask * ( (silu(gate) * value) · W2ᵀ ),  [value|gate] = LayerNorm(x) · W1ᵀ,
