@@ -41,7 +41,11 @@ WORKLOADS = {
                  desc="start+end TriangleAttention + transition, z[64,256,256,128] bf16, valid ~U{160..256} (BASELINE config 3)"),
     "n768": dict(B=1, N=768, valid="768", transition=True,
                  desc="start+end TriangleAttention + transition, z[1,768,768,128] bf16, all valid (pair track of BASELINE config 4)"),
+    "cfg5": dict(B=1, N=4096, valid="3900", transition=True, sharded=True, blocks=4,
+                 desc="4 x (start node, all-to-all, end node, transition), z[1,4096,4096,128] bf16 row-sharded over the "
+                      "GPUs, 3900 valid tokens (BASELINE config 5)"),
 }
+DEFAULT_STEPS = {"cfg2": 100, "cfg3": 20, "n768": 50, "cfg5": 3}
 
 
 def valid_lengths(spec: str, B: int, N: int, gen: torch.Generator) -> list[int]:
@@ -73,7 +77,7 @@ def measured_peaks() -> tuple[float, float, str]:
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons (NVML, else nvidia-smi) while the timed region runs."""
 
     def __init__(self, index: int):
         self.index = index
@@ -81,7 +85,35 @@ class ClockSampler:
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
 
+    def _run_nvml(self) -> bool:
+        """Reads the same fields through NVML in-process (a sample takes well under a millisecond)."""
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = int(visible.split(",")[self.index]) if visible and visible.split(",")[self.index].isdigit() else self.index
+            h = nv.nvmlDeviceGetHandleByIndex(index)
+            max_sm = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            names = (("hw_slowdown", nv.nvmlClocksThrottleReasonHwSlowdown),
+                     ("hw_thermal_slowdown", nv.nvmlClocksThrottleReasonHwThermalSlowdown),
+                     ("sw_thermal_slowdown", nv.nvmlClocksThrottleReasonSwThermalSlowdown),
+                     ("sw_power_cap", nv.nvmlClocksThrottleReasonSwPowerCap))
+        except Exception:
+            return False
+        while not self._stop.is_set():
+            try:
+                sm = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append((sm, max_sm, ",".join(n for n, bit in names if mask & bit)))
+            except Exception:
+                pass
+            self._stop.wait(0.005)
+        return True
+
     def _run(self):
+        if self._run_nvml():
+            return
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         while not self._stop.is_set():
@@ -268,8 +300,150 @@ def run_ours(args) -> dict:
     return result if rank == 0 else {}
 
 
+def run_sharded(args) -> dict:
+    """BASELINE config 5: one pair tensor z[1, 4096, 4096, 128] (3900 valid tokens) row-sharded over the ranks,
+    4 pair-track blocks of start node -> all-to-all -> end node -> transition (-> all-to-all back).  The total work
+    is fixed (strong scaling); with one rank the same blocks run on the whole tensor without any exchange."""
+    import torch.distributed as dist
+
+    import bionemo_inference_runtime_b200 as b200
+    from bionemo_inference_runtime_b200 import _lib, ops, sharded
+    from oracle import triangle_oracle as orc  # seeded weight recipe only
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    cfg = WORKLOADS[args.workload]
+    N, valid, nblocks = cfg["N"], int(cfg["valid"]), cfg["blocks"]
+    n = N // world
+    gen = torch.Generator(device=device).manual_seed(2000 + rank)
+    z_rows = torch.empty(1, n, N, 128, dtype=torch.bfloat16, device=device)
+    for r0 in range(0, n, 256):  # generate in slabs: keeps the fp32 temporary small
+        z_rows[:, r0:r0 + 256] = torch.randn(1, min(256, n - r0), N, 128, generator=gen, device=device).bfloat16()
+    idx = torch.arange(rank * n, (rank + 1) * n, device=device)
+    lengths_local = torch.where(idx < valid, valid, 0).to(torch.int32).reshape(1, n)  # m (x) m mask, rows == cols
+
+    blocks = []
+    for k in range(nblocks):
+        start, end, trans = build_modules(orc.make_node_weights(3000 + 3 * k), orc.make_node_weights(3001 + 3 * k),
+                                          orc.make_transition_weights(3002 + 3 * k), device)
+        blocks.append((start, end, trans))
+    if world > 1:
+        drivers = [sharded.ShardedPairBlock(s, e, t) for s, e, t in blocks]
+
+        def step(z):
+            for d in drivers:
+                z = d(z, lengths_local, lengths_local)
+            return z
+    else:
+        full_lengths = lengths_local
+
+        def step(z):
+            for s, e, t in blocks:
+                z = s(z, mask_bias=full_lengths, residual=True, inplace_residual=True)
+                z = e(z, mask_bias=full_lengths, residual=True, inplace_residual=True)
+                z = t(z, residual=True, inplace=True)
+            return z
+
+    flops_total = nblocks * (2 * node_flops(valid) + transition_flops(valid))
+    launches = nblocks * 7
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    work = z_rows.clone()
+    for _ in range(max(args.warmup, 3)):
+        work.copy_(z_rows)
+        step(work)
+    barrier()
+    times = []
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        for _ in range(args.steps):
+            work.copy_(z_rows)  # fresh input (the blocks work in place); the 4.3 GB / G copy also evicts L2
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step(work)
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+        barrier()
+    ms = sum(times) / len(times)
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel abandoned a bounded wait during the benchmark")
+
+    z_pin = z_rows.cpu().pin_memory()
+    out_pin = torch.empty_like(z_pin).pin_memory()
+    e2e_times = []
+    for i in range(1 + min(args.steps, 3)):
+        barrier()
+        t0 = time.perf_counter()
+        zd = z_pin.to(device, non_blocking=True)
+        out_pin.copy_(step(zd), non_blocking=True)
+        barrier()
+        if i >= 1:
+            e2e_times.append((time.perf_counter() - t0) * 1e3)
+    e2e_ms = sum(e2e_times) / len(e2e_times)
+
+    # dominant kernel on this rank's shard of the first block's starting node
+    start = blocks[0][0]
+    packed = start._packed(device)
+    bias_loc = torch.empty((1, 4, n, ops.pad8(N)), dtype=torch.bfloat16, device=device)
+    qkvg, bias_loc = ops.prologue(z_rows, packed, bias=bias_loc)
+    bias_full = sharded.gather_bias(bias_loc) if world > 1 else bias_loc
+    og = torch.empty(1, n, N, 128, dtype=torch.bfloat16, device=device)
+    ktimes = []
+    for i in range(4):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.attention(qkvg, bias_full, lengths_local, 1, n, N, out=og)
+        e1.record()
+        e1.synchronize()
+        if i >= 1:
+            ktimes.append(e0.elapsed_time(e1))
+    attn_ms = sum(ktimes) / len(ktimes)
+    attn_flops = float((lengths_local > 0).sum().item()) * valid * 512.0 * valid
+    peak_tf, _, peak_kind = measured_peaks()
+
+    stats = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = stats.tolist()
+    shard_bytes = z_rows.numel() * 2
+    a2a_bytes = 0 if world == 1 else int(shard_bytes * (world - 1) / world)
+    result = {
+        "metric": "tri_attn_tflops", "value": flops_total / ms / 1e9, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}", "tokens": N, "valid_lengths": cfg["valid"],
+                   "blocks": nblocks, "block_ms": ms / nblocks, "l2": "inputs far larger than L2 (4.3 GB pair tensor)",
+                   "empty_row_mode": "uniform",
+                   "parallelism": f"pair rows sharded x{world}; per block 2 all-to-all of {a2a_bytes} B per rank and "
+                                  f"2 all-gathers of the triangle bias" if world > 1 else "single GPU, no exchange"},
+        "e2e": {"value": flops_total / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": shard_bytes, "d2h_bytes_per_step": shard_bytes},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"kernel": "attention_kernel", "bound": "tensor", "achieved": attn_flops / attn_ms / 1e9,
+                     "peak": peak_tf, "unit": "TFLOP/s", "frac": attn_flops / attn_ms / 1e9 / peak_tf,
+                     "peak_source": f"{peak_kind} bf16 burst", "ms_per_launch": attn_ms, "traffic": None,
+                     "note": "rank 0's shard of one starting node"},
+        "clocks": clocks.summary(),
+    }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum per attention launch, from the committed ncu summaries (profiles/)
-TRAFFIC: dict[str, float | None] = {"cfg2": None, "cfg3": None, "n768": None}
+TRAFFIC: dict[str, float | None] = {"cfg2": 334.8e6, "cfg3": None, "n768": None}
 
 
 def cpu_sample(cfg: dict, rows: int, threads: int):
@@ -344,13 +518,20 @@ def run_reference(args) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default depends on the workload)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.steps is None:
+        args.steps = DEFAULT_STEPS[args.workload] if args.impl == "ours" else 5
+    if args.impl == "reference":
+        result = run_reference(args)
+    elif WORKLOADS[args.workload].get("sharded"):
+        result = run_sharded(args)
+    else:
+        result = run_ours(args)
     if result:
         print(json.dumps(result), flush=True)
 

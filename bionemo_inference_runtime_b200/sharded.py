@@ -1,0 +1,140 @@
+"""Row-sharded pair track for one multi-GPU box: one pair tensor split over the ranks of a process group.
+
+The reference has no distributed compute (its multi-GPU mode is whole-model replicas); this module adds the
+DAP-style partition its long-complex case needs.  One process per GPU, ``torch.distributed`` (NCCL) for the
+exchanges, the library's kernels for everything else.
+
+Layouts of the local shard of ``z[B, N, N, c]`` on rank ``g`` of ``G`` (``N % G == 0``, ``n = N / G``):
+
+* ``ROWS``: ``z[:, g*n:(g+1)*n, :, :]``  -> tensor ``[B, n, N, c]``
+* ``COLS``: ``z[:, :, g*n:(g+1)*n, :]``  -> tensor ``[B, N, n, c]``
+
+Per block:
+
+1. starting node on the ROWS shard.  Pair rows attend independently *given* the triangle bias, and the bias row
+   ``bias[h, q, :]`` is a projection of pair row ``q``: every rank projects the bias rows of its own pair rows and
+   one all-gather (1/32 of the bytes of ``z``) completes the ``[H, N, N]`` bias everywhere.
+2. all-to-all ROWS -> COLS (the transpose between the nodes).
+3. ending node on the COLS shard: it works on the transposed pair tensor, so pair *columns* are its independent
+   rows; the kernels read the shard through swapped strides, and the same bias all-gather applies.
+4. transition on the COLS shard (position-wise, layout does not matter).
+5. all-to-all COLS -> ROWS for the next block (``keep_layout=True`` skips it for a caller that continues in COLS).
+
+The compute stages are looked up on a small ``stages`` object so that the orchestration (what is gathered, what
+is exchanged, which strides are used) can be exercised with CPU tensors and the ``gloo`` backend.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, ops
+
+ROWS = "rows"
+COLS = "cols"
+
+
+class KernelStages:
+    """The library's kernels as the four stages the driver composes (CUDA tensors only)."""
+
+    def prologue(self, node, x_kernel_order: torch.Tensor):
+        """``x`` in kernel order ``[B, R, S, c]`` (any strides) -> (qkvg planes, local bias rows ``[B, H, R, S_pad]``)."""
+        B, R, S, _ = x_kernel_order.shape
+        bias = torch.empty((B, ops.HEADS, R, ops.pad8(S)), dtype=torch.bfloat16, device=x_kernel_order.device)
+        return ops.prologue(x_kernel_order, node._packed(x_kernel_order.device), node.layer_norm.eps, bias=bias)
+
+    def attention(self, node, qkvg, bias_full, lengths, B, R, S):
+        mode = _lib.EMPTY_ROW_UNIFORM if node.empty_row_mode == "uniform" else _lib.EMPTY_ROW_ZEROS
+        return ops.attention(qkvg, bias_full, lengths, B, R, S, empty_row_mode=mode)
+
+    def epilogue(self, node, og, residual_kernel_order, out_kernel_order):
+        B, R, S, _ = og.shape
+        packed = node._packed(og.device)
+        r, o = residual_kernel_order, out_kernel_order
+        _lib.call("b200ta_epilogue", og.data_ptr(), og.stride(0), og.stride(1), og.stride(2), packed.data_ptr(),
+                  None if r is None else r.data_ptr(), *((0, 0, 0) if r is None else r.stride()[:3]),
+                  o.data_ptr(), *o.stride()[:3], B, R, S, torch.cuda.current_stream().cuda_stream)
+        return out_kernel_order
+
+    def transition(self, layer, x: torch.Tensor) -> torch.Tensor:
+        return layer(x, residual=True, inplace=True)
+
+
+def shard(z: torch.Tensor, rank: int, world: int, layout: str = ROWS) -> torch.Tensor:
+    """The contiguous local shard of a full pair tensor (for tests and for loading inputs)."""
+    n = z.shape[1] // world
+    if z.shape[1] % world or z.shape[1] != z.shape[2]:
+        raise ValueError(f"need a square pair tensor whose side is divisible by the world size, got {tuple(z.shape)}")
+    part = z[:, rank * n:(rank + 1) * n] if layout == ROWS else z[:, :, rank * n:(rank + 1) * n]
+    return part.contiguous()
+
+
+def exchange(x: torch.Tensor, to_layout: str, group=None) -> torch.Tensor:
+    """All-to-all between the ROWS shard ``[B, n, N, c]`` and the COLS shard ``[B, N, n, c]``.
+
+    Rank ``g`` sends the block (its rows, columns of rank ``p``) to rank ``p`` and receives (rows of rank ``p``, its
+    columns): ``(G-1)/G`` of the shard crosses the links once.  One staging copy packs the outgoing blocks per peer;
+    the received blocks already are the target layout.
+    """
+    world = dist.get_world_size(group)
+    B = x.shape[0]
+    c = x.shape[-1]
+    if to_layout == COLS:
+        n, N = x.shape[1], x.shape[2]
+        send = x.view(B, n, world, n, c).permute(2, 0, 1, 3, 4).contiguous()      # [G][B, n(i), n(j), c]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)                            # [G(src p)][B, n(i of p), n(j), c]
+        return recv.permute(1, 0, 2, 3, 4).reshape(B, N, n, c)                     # i = p*n + i_local: contiguous view
+    if to_layout == ROWS:
+        N, n = x.shape[1], x.shape[2]
+        send = x.view(B, world, n, n, c).permute(1, 0, 2, 3, 4).contiguous()      # [G(dst p)][B, n(i of p), n(j), c]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)                            # [G(src p)][B, n(i), n(j of p), c]
+        return recv.permute(1, 2, 0, 3, 4).reshape(B, n, N, c)                     # j = p*n + j_local (one copy)
+    raise ValueError(f"unknown layout {to_layout!r}")
+
+
+def gather_bias(bias_local: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather of the locally projected bias rows ``[B, H, n, S_pad]`` into the full ``[B, H, N, S_pad]``."""
+    world = dist.get_world_size(group)
+    B, H, n, sp = bias_local.shape
+    gathered = torch.empty((world, B, H, n, sp), dtype=bias_local.dtype, device=bias_local.device)
+    dist.all_gather_into_tensor(gathered.view(-1), bias_local.contiguous().view(-1), group=group)
+    return gathered.permute(1, 2, 0, 3, 4).reshape(B, H, world * n, sp)
+
+
+class ShardedPairBlock:
+    """start node -> exchange -> end node -> transition (-> exchange back) on a sharded pair tensor."""
+
+    def __init__(self, start_node, end_node, transition=None, group=None, stages=None):
+        self.start_node = start_node
+        self.end_node = end_node
+        self.transition = transition
+        self.group = group
+        self.stages = stages if stages is not None else KernelStages()
+
+    def _node(self, node, x_shard: torch.Tensor, layout: str, lengths_local: torch.Tensor | None) -> torch.Tensor:
+        """One node on the shard whose independent rows are local: ROWS for the starting node, COLS for the ending
+        node.  ``lengths_local`` holds the valid-key count of each local kernel row, ``[B, n]`` int32."""
+        xk = x_shard if layout == ROWS else x_shard.transpose(1, 2)  # kernel order [B, R = n, S = N, c]
+        B, R, S, _ = xk.shape
+        qkvg, bias_local = self.stages.prologue(node, xk)
+        bias_full = gather_bias(bias_local, self.group)
+        og = self.stages.attention(node, qkvg, bias_full, lengths_local, B, R, S)
+        self.stages.epilogue(node, og, xk, xk)  # in place: z += update
+        return x_shard
+
+    def forward(self, z_rows: torch.Tensor, lengths_rows: torch.Tensor | None = None,
+                lengths_cols: torch.Tensor | None = None, keep_layout: bool = False) -> torch.Tensor:
+        """``z_rows``: ROWS shard ``[B, n, N, c]`` (updated in place where possible).  ``lengths_rows[b, i_local]`` =
+        valid keys of local pair row i (starting node); ``lengths_cols[b, j_local]`` = valid keys of local pair column
+        j (ending node).  Returns the ROWS shard of the block output (the COLS shard with ``keep_layout``)."""
+        z_rows = self._node(self.start_node, z_rows, ROWS, lengths_rows)
+        z_cols = exchange(z_rows, COLS, self.group)
+        z_cols = self._node(self.end_node, z_cols, COLS, lengths_cols)
+        if self.transition is not None:
+            z_cols = self.stages.transition(self.transition, z_cols)
+        return z_cols if keep_layout else exchange(z_cols, ROWS, self.group)
+
+    __call__ = forward
