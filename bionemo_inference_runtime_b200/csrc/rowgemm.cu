@@ -1,18 +1,18 @@
 // Row-tile GEMM kernels of the triangle-attention node (sm_100a).
 //
-// One persistent CTA per SM walks 128-position tiles of the pair tensor.  For each
-// tile the 128x128 bf16 activation block arrives by TMA as the K-major A operand,
-// the weights (resident in shared memory for the whole kernel) are the B operand,
-// tcgen05.mma accumulates into TMEM and four epilogue warps (one TMEM lane = one
-// position = one thread) finish the rows and hand them to TMA stores.
+// One persistent CTA per SM walks 128-position tiles of the pair tensor.  For each tile the 128x128 bf16
+// activation block arrives by TMA as the K-major A operand, the weights (resident in shared memory for the
+// whole kernel) are the B operand, tcgen05.mma accumulates into TMEM and eight epilogue warps (one TMEM lane =
+// one position = one thread per warpgroup, the two warpgroups take alternate 32-column groups) finish the rows
+// and store them with 16-byte vector stores (64 contiguous bytes per thread and group).
 //
-//   kPrologue: z tile -> LayerNorm statistics (from the smem copy) while the tensor
-//              core multiplies the raw rows with the LayerNorm-folded weights:
-//              q,k,v,g (512 columns, written head-major) and 4 triangle-bias heads.
+//   kPrologue: z tile -> LayerNorm statistics (from the smem copy) while the tensor core multiplies the raw
+//              rows with the LayerNorm-folded weights: q,k,v,g (512 columns, written head-major) and 4
+//              triangle-bias heads.
 //   kEpilogue: og tile -> og · W_oᵀ + b_o + residual.
 //
-// Warp roles: warps 0-3 epilogue (TMEM lanes 32w..32w+31), warp 4 TMA producer,
-// warp 5 MMA issuer / TMEM owner.
+// Warp roles (320 threads): warps 0-7 epilogue (TMEM lanes 32(w%4)..+31), warp 8 TMA producer, warp 9 MMA
+// issuer / TMEM owner.
 #include "common.cuh"
 #include "layout.h"
 
@@ -20,10 +20,8 @@ namespace b200ta {
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
 constexpr int kSlotCols = 256;  // TMEM columns per accumulator slot (2 slots)
-constexpr int kOutSlab = 2048;  // one warp's [32 rows][32 cols] bf16 staging slab
-constexpr int kOutSlots = 3;
 
 enum Mode { kPrologue = 0, kEpilogue = 1 };
 
@@ -37,6 +35,9 @@ struct RowGemmParams {
   float eps;
   __nv_bfloat16* bias;
   long long bs_b, bs_h, bs_q, bs_k;
+  __nv_bfloat16* out;                         // prologue: q/k/v/g planes; epilogue: output pair tensor
+  long long qs_which, qs_br, qs_h, qs_s;      // prologue strides (elements)
+  long long os_b, os_r, os_s;                 // epilogue strides (elements)
   int want_qkvg;
   int has_residual;
   int* status;
@@ -47,11 +48,11 @@ struct Smem {
   static constexpr int kWRows = MODE == kPrologue ? kNodeRows : kC;
   static constexpr int kWHalf = kWRows * 128;  // bytes of one 64-channel half
   static constexpr int kW = 0;
-  static constexpr int kA = kW + 2 * kWHalf;               // 2 stages x 32 KiB
-  static constexpr int kRes = kA + 2 * 32768;              // epilogue only: 2 stages x 32 KiB
-  static constexpr int kOut = kRes + (MODE == kEpilogue ? 2 * 32768 : 0);
-  static constexpr int kVec = kOut + 4 * kOutSlots * kOutSlab;  // sc (prologue) or bo (epilogue)
-  static constexpr int kVecBytes = MODE == kPrologue ? kNodeRows * 8 : kC * 4;
+  static constexpr int kA = kW + 2 * kWHalf;   // 2 stages x 32 KiB
+  static constexpr int kRes = kA + 2 * 32768;  // epilogue only: 2 stages x 32 KiB
+  static constexpr int kVec = kRes + (MODE == kEpilogue ? 2 * 32768 : 0);
+  // prologue: per column pair {rowsum0, rowsum1, const0, const1}; epilogue: b_o
+  static constexpr int kVecBytes = MODE == kPrologue ? (kNodeRows / 2) * 16 : kC * 4;
   static constexpr int kBars = kVec + kVecBytes;
   static constexpr int kTotal = kBars + 128;
   static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
@@ -60,11 +61,14 @@ struct Smem {
 // barrier slots inside the kBars block (8 bytes each)
 enum Bar { W_FULL = 0, A_FULL = 1, A_EMPTY = 3, ACC_FULL = 5, ACC_EMPTY = 7, NUM_BARS = 9 };
 
+__device__ __forceinline__ void stg128(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(a, b, c, d);
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-               const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res,
-               const RowGemmParams p) {
+               const __grid_constant__ CUtensorMap tm_res, const RowGemmParams p) {
   using L = Smem<MODE>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -84,21 +88,24 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     mbar_init(bars + W_FULL * 8, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + (A_FULL + i) * 8, 1);
-      mbar_init(bars + (A_EMPTY + i) * 8, 5);  // 4 epilogue warps + the MMA commit
+      mbar_init(bars + (A_EMPTY + i) * 8, 9);  // 8 epilogue warps + the MMA commit
       mbar_init(bars + (ACC_FULL + i) * 8, 1);
-      mbar_init(bars + (ACC_EMPTY + i) * 8, 4);
+      mbar_init(bars + (ACC_EMPTY + i) * 8, 8);
     }
     fence_mbar_init();
   }
   // stage the per-column vectors
   if (MODE == kPrologue) {
-    float2* dst = reinterpret_cast<float2*>(gen + L::kVec);
-    for (int i = threadIdx.x; i < kNodeRows; i += kThreads) dst[i] = p.sc[i];
+    float4* dst = reinterpret_cast<float4*>(gen + L::kVec);
+    for (int i = threadIdx.x; i < kNodeRows / 2; i += kThreads) {
+      const float2 a = p.sc[2 * i], b = p.sc[2 * i + 1];
+      dst[i] = make_float4(a.x, b.x, a.y, b.y);
+    }
   } else {
     float* dst = reinterpret_cast<float*>(gen + L::kVec);
     for (int i = threadIdx.x; i < kC; i += kThreads) dst[i] = p.bo[i];
   }
-  if (warp == 5) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+  if (warp == 9) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -106,12 +113,11 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
   const int my_tiles = (p.num_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1;  // blockIdx.x < num_tiles
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------- TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tm_a);
       tma_prefetch_desc(&tm_w);
-      tma_prefetch_desc(&tm_out);
       mbar_expect_tx(bars + W_FULL * 8, 2 * L::kWHalf);
       constexpr int kBoxRows = MODE == kPrologue ? 176 : 128;
       for (int kh = 0; kh < 2; ++kh)
@@ -142,7 +148,7 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         mbar_wait(bars + (A_FULL + (last & 1)) * 8, (last >> 1) & 1, abort_flag + 1);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       bool ok = mbar_wait(bars + W_FULL * 8, 0, abort_flag);
@@ -175,10 +181,11 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
   } else {
     // ------------------------------------------------------------- epilogue warps
-    const int m = warp * 32 + lane;  // row of the tile == TMEM lane
-    const uint32_t lane_taddr = tmem_base + (uint32_t(warp * 32) << 16);
-    const uint32_t slab0 = base + L::kOut + warp * kOutSlots * kOutSlab;
-    int uc = 0, sc_count = 0;
+    const int e = warp >> 2;               // which alternate column groups this warpgroup takes
+    const int m = (warp & 3) * 32 + lane;  // row of the tile == TMEM lane
+    const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
+    const bool normalize = MODE == kPrologue && __ldg(p.flags) != 0;
+    int uc = 0;
     bool ok = true;
     for (int i = 0; ok && i < my_tiles; ++i) {
       const int tile = blockIdx.x + i * gridDim.x;
@@ -186,15 +193,11 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const int br = tile / p.tiles_s;
       const int r = br % p.R, b = br / p.R;
       const int stage = i & 1;
-      const int s_row0 = st * kTileM + warp * 32;  // first position of this warp's slab
+      const int s = st * kTileM + m;  // this thread's position along the sequence axis
       ok = mbar_wait(bars + (A_FULL + stage) * 8, (i >> 1) & 1, abort_flag);
       if (!ok) break;
       float rstd = 1.f, nmr = 0.f;
-      if (MODE == kPrologue && __ldg(p.flags) == 0) {
-        // input already normalised: plain projection
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars + (A_EMPTY + stage) * 8);
-      } else if (MODE == kPrologue) {
+      if (normalize) {
         // LayerNorm statistics of row m from the swizzled smem copy of the z tile.
         uint32_t v[64];
         const uint32_t a0 = base + L::kA + stage * 32768;
@@ -203,22 +206,25 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           uint4 x = lds128(a0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
           v[c * 4 + 0] = x.x, v[c * 4 + 1] = x.y, v[c * 4 + 2] = x.z, v[c * 4 + 3] = x.w;
         }
-        float sum = 0.f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < 64; ++j) sum += bf16_lo(v[j]) + bf16_hi(v[j]);
-        const float mu = sum * (1.f / kC);
-        float var = 0.f;
+        for (int j = 0; j < 64; ++j) sum4[j & 3] += bf16_lo(v[j]) + bf16_hi(v[j]);
+        const float mu = ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3])) * (1.f / kC);
+        float var4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
           const float d0 = bf16_lo(v[j]) - mu, d1 = bf16_hi(v[j]) - mu;
-          var = fmaf(d0, d0, var);
-          var = fmaf(d1, d1, var);
+          var4[j & 3] = fmaf(d0, d0, var4[j & 3]);
+          var4[j & 3] = fmaf(d1, d1, var4[j & 3]);
         }
-        rstd = rsqrtf(var * (1.f / kC) + p.eps);
+        rstd = rsqrtf(((var4[0] + var4[1]) + (var4[2] + var4[3])) * (1.f / kC) + p.eps);
         nmr = -mu * rstd;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars + (A_EMPTY + stage) * 8);
       }
+      if (MODE == kPrologue) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + (A_EMPTY + stage) * 8);  // done reading the z tile
+      }
+      const uint64_t rstd2 = pack_f32x2(rstd, rstd), nmr2 = pack_f32x2(nmr, nmr);
       for (int u = u_begin; ok && u < u_end; ++u, ++uc) {
         const int slot = uc & 1;
         ok = mbar_wait(bars + (ACC_FULL + slot) * 8, (uc >> 1) & 1, abort_flag);
@@ -226,39 +232,49 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         tc_fence_after();
         const uint32_t acc_addr = lane_taddr + slot * kSlotCols;
         if (MODE == kPrologue && u == 2) {
-          // triangle-bias heads: columns 512..515 of the folded projection
-          uint32_t a[16];
-          tmem_ld16(acc_addr, a);
-          tmem_ld_wait();
-          const float2* sc = reinterpret_cast<const float2*>(gen + L::kVec) + 512;
-          const int s = st * kTileM + m;
-          if (p.bias != nullptr && s < p.S_pad) {
+          // triangle-bias heads: columns 512..515 of the folded projection (first warpgroup only)
+          if (e == 0) {
+            uint32_t a[16];
+            tmem_ld16(acc_addr, a);
+            tmem_ld_wait();
+            const float4* sc4 = reinterpret_cast<const float4*>(gen + L::kVec) + 256;
+            if (p.bias != nullptr && s < p.S_pad) {
 #pragma unroll
-            for (int h = 0; h < kHeads; ++h) {
-              const float2 t = sc[h];
-              const float val = s < p.S ? fmaf(rstd, __uint_as_float(a[h]), fmaf(nmr, t.x, t.y)) : 0.f;
-              p.bias[b * p.bs_b + h * p.bs_h + r * p.bs_q + s * p.bs_k] = __float2bfloat16_rn(val);
+              for (int hp = 0; hp < 2; ++hp) {
+                const float4 t = sc4[hp];  // {rowsum0, rowsum1, const0, const1}
+                const float v0 = s < p.S ? fmaf(rstd, __uint_as_float(a[2 * hp]), fmaf(nmr, t.x, t.z)) : 0.f;
+                const float v1 = s < p.S ? fmaf(rstd, __uint_as_float(a[2 * hp + 1]), fmaf(nmr, t.y, t.w)) : 0.f;
+                p.bias[b * p.bs_b + (2 * hp) * p.bs_h + r * p.bs_q + s * p.bs_k] = __float2bfloat16_rn(v0);
+                p.bias[b * p.bs_b + (2 * hp + 1) * p.bs_h + r * p.bs_q + s * p.bs_k] = __float2bfloat16_rn(v1);
+              }
             }
           }
         } else {
           const int ngroups = MODE == kPrologue ? 8 : 4;
-          for (int g = 0; g < ngroups; ++g, ++sc_count) {
+          for (int g = e; g < ngroups; g += 2) {
             uint32_t a[32];
             tmem_ld32(acc_addr + g * 32, a);
-            tmem_ld_wait();
-            const uint32_t slab = slab0 + (sc_count % kOutSlots) * kOutSlab;
-            if (lane == 0) tma_store_wait_read<kOutSlots - 1>();
-            __syncwarp();
             const int n0 = (MODE == kPrologue ? u * 256 : 0) + g * 32;
             uint32_t packed[16];
             if (MODE == kPrologue) {
-              const float2* sc = reinterpret_cast<const float2*>(gen + L::kVec) + n0;
+              const float4* sc4 = reinterpret_cast<const float4*>(gen + L::kVec) + (n0 >> 1);
+              tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const float2 t0 = sc[2 * j], t1 = sc[2 * j + 1];
-                const float o0 = fmaf(rstd, __uint_as_float(a[2 * j]), fmaf(nmr, t0.x, t0.y));
-                const float o1 = fmaf(rstd, __uint_as_float(a[2 * j + 1]), fmaf(nmr, t1.x, t1.y));
+                const float4 t = sc4[j];  // {rowsum0, rowsum1, const0, const1} of columns n0+2j, n0+2j+1
+                const uint64_t off = fma_f32x2(nmr2, pack_f32x2(t.x, t.y), pack_f32x2(t.z, t.w));
+                float o0, o1;
+                unpack_f32x2(fma_f32x2(rstd2, pack_f32x2(__uint_as_float(a[2 * j]), __uint_as_float(a[2 * j + 1])), off),
+                             o0, o1);
                 packed[j] = pack_bf16x2(o0, o1);
+              }
+              if (s < p.S) {
+                // head-major planes: 64 contiguous bytes per (plane, head, position)
+                __nv_bfloat16* dst = p.out + (n0 >> 7) * p.qs_which + (long long)br * p.qs_br + ((n0 >> 5) & 3) * p.qs_h +
+                                     (long long)s * p.qs_s;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                  stg128(dst + c * 8, packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
               }
             } else {
               const float* bo = reinterpret_cast<const float*>(gen + L::kVec) + n0;
@@ -274,27 +290,19 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 16; ++j) res[j] = 0u;
               }
+              tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const float o0 = __uint_as_float(a[2 * j]) + bo[2 * j] + bf16_lo(res[j]);
                 const float o1 = __uint_as_float(a[2 * j + 1]) + bo[2 * j + 1] + bf16_hi(res[j]);
                 packed[j] = pack_bf16x2(o0, o1);
               }
-            }
+              if (s < p.S) {
+                __nv_bfloat16* dst = p.out + b * p.os_b + r * p.os_r + (long long)s * p.os_s + n0;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-              sts128(slab + sw64_offset(lane, c),
-                     make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]));
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (s_row0 < p.S) {
-                if (MODE == kPrologue)
-                  tma_store_5d(&tm_out, slab, 0, s_row0, (n0 >> 5) & 3, br, n0 >> 7);
-                else
-                  tma_store_4d(&tm_out, slab, n0, s_row0, r, b);
+                for (int c = 0; c < 4; ++c)
+                  stg128(dst + c * 8, packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
               }
-              tma_store_commit();
             }
           }
         }
@@ -304,16 +312,15 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       }
       if (MODE == kEpilogue) {
         __syncwarp();
-        if (lane == 0) mbar_arrive(bars + (A_EMPTY + stage) * 8);
+        if (lane == 0) mbar_arrive(bars + (A_EMPTY + stage) * 8);  // done reading the residual tile
       }
     }
-    if (lane == 0) tma_store_wait_all();
   }
 
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -354,11 +361,17 @@ int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
   B200TA_REQUIRE(int64_t(B) * R < (int64_t(1) << 31), "prologue: B*R too large");
   int rc = check_strides("prologue z", zs_b, zs_r, zs_s);
   if (rc != B200TA_OK) return rc;
+  if (want_qkvg) {
+    rc = check_strides("prologue qkvg", qs_which, qs_br, qs_h);
+    if (rc != B200TA_OK) return rc;
+    B200TA_REQUIRE(qs_s % 8 == 0 && qs_s > 0, "prologue qkvg: s stride must be a positive multiple of 8");
+    B200TA_REQUIRE((reinterpret_cast<uintptr_t>(qkvg) & 15u) == 0, "prologue: qkvg must be 16-byte aligned");
+  }
   DeviceState* st = nullptr;
   rc = get_device_state(&st);
   if (rc != B200TA_OK) return rc;
 
-  CUtensorMap tm_a, tm_w, tm_out;
+  CUtensorMap tm_a, tm_w;
   rc = pair_tensor_map(&tm_a, z, zs_b, zs_r, zs_s, B, R, S, 64, kTileM, SWZ_128, "prologue z");
   if (rc != B200TA_OK) return rc;
   const char* pk = static_cast<const char*>(packed);
@@ -368,18 +381,6 @@ int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
     uint32_t box[2] = {64, 176};
     rc = encode_tensor_map(&tm_w, pk + kNodeWOff, 2, 2, dims, strides, box, SWZ_128, "prologue weights");
     if (rc != B200TA_OK) return rc;
-  }
-  if (want_qkvg) {
-    rc = check_strides("prologue qkvg", qs_which, qs_br, qs_h);
-    if (rc != B200TA_OK) return rc;
-    B200TA_REQUIRE(qs_s % 8 == 0 && qs_s > 0, "prologue qkvg: s stride must be a positive multiple of 8");
-    uint64_t dims[5] = {uint64_t(kHeadDim), uint64_t(S), uint64_t(kHeads), uint64_t(B) * R, 4};
-    uint64_t strides[4] = {uint64_t(qs_s) * 2, uint64_t(qs_h) * 2, uint64_t(qs_br) * 2, uint64_t(qs_which) * 2};
-    uint32_t box[5] = {32, 32, 1, 1, 1};
-    rc = encode_tensor_map(&tm_out, qkvg, 2, 5, dims, strides, box, SWZ_64, "prologue qkvg");
-    if (rc != B200TA_OK) return rc;
-  } else {
-    tm_out = tm_a;  // never used
   }
 
   RowGemmParams p{};
@@ -391,13 +392,15 @@ int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
   p.eps = eps;
   p.bias = static_cast<__nv_bfloat16*>(bias);
   p.bs_b = bs_b, p.bs_h = bs_h, p.bs_q = bs_q, p.bs_k = bs_k;
+  p.out = static_cast<__nv_bfloat16*>(qkvg);
+  p.qs_which = qs_which, p.qs_br = qs_br, p.qs_h = qs_h, p.qs_s = qs_s;
   p.want_qkvg = want_qkvg ? 1 : 0;
   p.status = st->status_dev;
 
   auto kern = rowgemm_kernel<kPrologue>;
   B200TA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<kPrologue>::kDynamic));
   const int grid = p.num_tiles < st->num_sms ? p.num_tiles : st->num_sms;
-  kern<<<grid, kThreads, Smem<kPrologue>::kDynamic, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_w, tm_out, tm_a, p);
+  kern<<<grid, kThreads, Smem<kPrologue>::kDynamic, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_w, tm_a, p);
   B200TA_CHECK_CUDA(cudaGetLastError());
   return B200TA_OK;
 }
@@ -409,6 +412,7 @@ int b200ta_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, co
   B200TA_REQUIRE(og && packed && out, "epilogue: NULL pointer");
   B200TA_REQUIRE(B > 0 && R > 0 && S > 0, "epilogue: bad sizes B=%d R=%d S=%d", B, R, S);
   B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "epilogue: packed must be 256-byte aligned");
+  B200TA_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15u) == 0, "epilogue: out must be 16-byte aligned");
   int rc = check_strides("epilogue og", gs_b, gs_r, gs_s);
   if (rc == B200TA_OK) rc = check_strides("epilogue out", os_b, os_r, os_s);
   if (rc == B200TA_OK && residual) rc = check_strides("epilogue residual", rs_b, rs_r, rs_s);
@@ -417,7 +421,7 @@ int b200ta_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, co
   rc = get_device_state(&st);
   if (rc != B200TA_OK) return rc;
 
-  CUtensorMap tm_a, tm_w, tm_out, tm_res;
+  CUtensorMap tm_a, tm_w, tm_res;
   rc = pair_tensor_map(&tm_a, og, gs_b, gs_r, gs_s, B, R, S, 64, kTileM, SWZ_128, "epilogue og");
   if (rc != B200TA_OK) return rc;
   const char* pk = static_cast<const char*>(packed);
@@ -428,8 +432,6 @@ int b200ta_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, co
     rc = encode_tensor_map(&tm_w, pk + kNodeWoOff, 2, 2, dims, strides, box, SWZ_128, "epilogue weights");
     if (rc != B200TA_OK) return rc;
   }
-  rc = pair_tensor_map(&tm_out, out, os_b, os_r, os_s, B, R, S, 32, 32, SWZ_64, "epilogue out");
-  if (rc != B200TA_OK) return rc;
   if (residual) {
     rc = pair_tensor_map(&tm_res, residual, rs_b, rs_r, rs_s, B, R, S, 32, kTileM, SWZ_64, "epilogue residual");
     if (rc != B200TA_OK) return rc;
@@ -442,13 +444,16 @@ int b200ta_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, co
   p.tiles_s = (S + kTileM - 1) / kTileM;
   p.num_tiles = B * R * p.tiles_s;
   p.bo = reinterpret_cast<const float*>(pk + kNodeBoOff);
+  p.flags = reinterpret_cast<const int*>(pk + kNodeFlagsOff);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.os_b = os_b, p.os_r = os_r, p.os_s = os_s;
   p.has_residual = residual ? 1 : 0;
   p.status = st->status_dev;
 
   auto kern = rowgemm_kernel<kEpilogue>;
   B200TA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<kEpilogue>::kDynamic));
   const int grid = p.num_tiles < st->num_sms ? p.num_tiles : st->num_sms;
-  kern<<<grid, kThreads, Smem<kEpilogue>::kDynamic, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_w, tm_out, tm_res, p);
+  kern<<<grid, kThreads, Smem<kEpilogue>::kDynamic, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_w, tm_res, p);
   B200TA_CHECK_CUDA(cudaGetLastError());
   return B200TA_OK;
 }
