@@ -370,8 +370,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint64_t c2 = pack_f32x2(c, c);
     int ct = 0;  // tiles this half has processed (phase of S_FULL / O_FULL)
     bool ok = true;
+    Item nxt = decode_item(p, blockIdx.x);
     for (int i = 0; ok && i < my_items; ++i) {
-      const Item it = decode_item(p, blockIdx.x + i * gridDim.x);
+      const Item it = nxt;
+      // fetch the next item's row length now: its global-memory latency hides behind this item's work
+      if (i + 1 < my_items) nxt = decode_item(p, blockIdx.x + (i + 1) * gridDim.x);
       const int q = it.q0 + w * kQTile + m;  // query position
       __nv_bfloat16* out_row = p.out + it.br * p.o_br + (long long)q * p.o_s + it.h * p.o_h;
       if (it.skip) {
@@ -455,10 +458,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             const int j0 = qtr * 32 + 2 * e;
+            const uint64_t d2 = fma_f32x2(pack_f32x2(s2[j0], s2[j0 + 1]), c2, nmc2);
             float d0, d1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(s2[j0], s2[j0 + 1]), c2, nmc2), d0, d1);
-            const float p0 = ex2_approx(d0), p1 = ex2_approx(d1);
-            sum2[e & 3] = add_f32x2(sum2[e & 3], pack_f32x2(p0, p1));
+            unpack_f32x2(d2, d0, d1);
+            const uint64_t p2 = pack_f32x2(ex2_approx(d0), ex2_approx(d1));
+            sum2[e & 3] = add_f32x2(sum2[e & 3], p2);
+            float p0, p1;
+            unpack_f32x2(p2, p0, p1);
             pk[e] = pack_bf16x2(p0, p1);
           }
           tmem_st16(p_addr + qtr * 16, pk);
@@ -474,38 +480,42 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (lane == 0) mbar_arrive(bars + (P_FULL + w) * 8);
       }
       if (!ok) break;
-      // the item's output: O (in TMEM) / row_sum
+      // Gate factors first: they only need the gate row fetched during the last tile, and computing them here
+      // fills the time the last P·V takes.
+      float sg[32];
+      if (p.gate != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t gw[4] = {gv[j].x, gv[j].y, gv[j].z, gv[j].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            // sigmoid(x) = 0.5 * tanh(x / 2) + 0.5
+            sg[j * 8 + 2 * e] = fmaf(0.5f, tanh_approx(0.5f * bf16_lo(gw[e])), 0.5f);
+            sg[j * 8 + 2 * e + 1] = fmaf(0.5f, tanh_approx(0.5f * bf16_hi(gw[e])), 0.5f);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sg[j] = 1.f;
+      }
+      const float inv = 1.f / row_sum;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) sg[j] *= inv;
+      // the item's output: O (in TMEM) / row_sum * gate
       ok = mbar_wait(bars + (O_FULL + w) * 8, (ct - 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      float o[32];
+      uint32_t pk[16];
       {
         uint32_t t[32];
         tmem_ld32(o_addr, t);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(t[j]);
+        for (int j = 0; j < 16; ++j)
+          pk[j] = pack_bf16x2(__uint_as_float(t[2 * j]) * sg[2 * j], __uint_as_float(t[2 * j + 1]) * sg[2 * j + 1]);
       }
       tc_fence_before();
       if (q < p.S) {
-        const float inv = 1.f / row_sum;
-        uint32_t pk[16];
-        if (p.gate != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t gw[4] = {gv[j].x, gv[j].y, gv[j].z, gv[j].w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              // sigmoid(x) = 0.5 * tanh(x / 2) + 0.5
-              const float s0 = fmaf(0.5f, tanh_approx(0.5f * bf16_lo(gw[e])), 0.5f);
-              const float s1 = fmaf(0.5f, tanh_approx(0.5f * bf16_hi(gw[e])), 0.5f);
-              pk[j * 4 + e] = pack_bf16x2(o[j * 8 + 2 * e] * inv * s0, o[j * 8 + 2 * e + 1] * inv * s1);
-            }
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) pk[j] = pack_bf16x2(o[2 * j] * inv, o[2 * j + 1] * inv);
-        }
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           reinterpret_cast<uint4*>(out_row)[j] = make_uint4(pk[j * 4], pk[j * 4 + 1], pk[j * 4 + 2], pk[j * 4 + 3]);
