@@ -1,8 +1,9 @@
 // Triangle attention core for sm_100a: flash-style, head_dim 32, bf16 in, fp32 softmax.
 //
 // For every pair row (b, r), head h and query s:
-//   o[s,:] = softmax_t( scale * (q[s]·k[t] + bias[b,h,s,t]) ; t < len[b,r] ) · v[t,:]   (* sigmoid(gate[s,:]))
-// where `bias` is the triangle bias already divided by `scale` (the prologue writes it that way).
+//   o[s,:] = softmax_t( scale * (q[s]·k[t] + bias[b,h,s,t]) ; t < len[b,r] ) · v[t,:]   (* gate[s,:])
+// where `bias` is the triangle bias already divided by `scale` and `gate` holds sigmoid(gate logits) (the
+// prologue writes both that way).
 // The N x N x N logits never exist in memory: a CTA owns 256 queries of one (b, r, h), walks the
 // keys in tiles of 128 and keeps a running max / sum per query and the output in TMEM.
 //
@@ -11,10 +12,11 @@
 //   tcgen05  S  = Q·Kᵀ          (128x128x32, K-major operands in smem, accumulator in TMEM)
 //   tcgen05  S += I·Bias        (128x128x128: the identity, resident in TMEM as the A operand, times the
 //                                bias tile as MN-major B operand - the bias add costs no CUDA-core work)
-//   softmax  one thread per query row: S from TMEM -> registers, running max (lazily updated), exp2,
-//            row sum; the bf16 probabilities go straight back to TMEM
+//   softmax  one thread per query row: S from TMEM -> registers, exp2 relative to the maximum of the row's
+//            first key tile, row sum; the bf16 probabilities go straight back to TMEM
 //   tcgen05  O += P·V           (128x32x128: P is the A operand from TMEM, V the MN-major B operand from
-//                                its [key][d] tile); O is only rescaled when the running max moved
+//                                its [key][d] tile); O is only rescaled when a tile's sum would leave the
+//                                safe fp32 range
 // The two 128-query halves are handled by two softmax warpgroups that share K/V and alternate on the
 // tensor core.  The MMA warp runs one key tile ahead (also across work items), so the next scores are
 // in TMEM before a warpgroup asks for them.
@@ -32,11 +34,12 @@ constexpr int kThreads = 384;
 constexpr int kQTile = 128;  // queries per softmax warpgroup
 constexpr int kKTile = 128;  // keys per tile
 constexpr int kStages = 2;
-constexpr float kRescaleThreshold = 8.f;  // log2 units: O is rescaled only when the max grew by more than 2^8
+constexpr float kRebaseSum = 1.2676506e30f;  // 2^100: a tile sum at or above this moves the reference point
 
 struct AttnParams {
   int B, R, S, S_pad;
   int q_pairs;    // ceil(S / 256)
+  uint32_t r_mul, r_shr, qp_mul, qp_shr;  // division by R and by q_pairs as multiply-high and shift
   int num_items;  // B * 4 * q_pairs * R
   const int32_t* lengths;
   long long ls_b, ls_r;
@@ -88,17 +91,31 @@ struct Item {
   bool skip;     // no valid key and "zeros" semantics: nothing to compute
 };
 
-__device__ __forceinline__ Item decode_item(const AttnParams& p, int item) {
+// n / d for n < 2^31 with the constants of fast_div_constants(); mul == 0 stands for d == 1.
+__device__ __forceinline__ int fast_div(int n, uint32_t mul, uint32_t shr) {
+  return mul ? int(__umulhi(uint32_t(n), mul) >> shr) : n;
+}
+
+// Row length of a work item as stored (not clamped yet).
+__device__ __forceinline__ int item_raw_length(const AttnParams& p, int item) {
+  if (p.lengths == nullptr) return p.S;
+  const int t = fast_div(item, p.r_mul, p.r_shr);
+  const int r = item - t * p.R;
+  const int b = fast_div(t, p.qp_mul, p.qp_shr) / kHeads;
+  return p.lengths[b * p.ls_b + r * p.ls_r];
+}
+
+__device__ __forceinline__ Item decode_item(const AttnParams& p, int item, int len) {
   Item it;
-  it.r = item % p.R;
-  int t = item / p.R;
-  const int qp = t % p.q_pairs;
-  t /= p.q_pairs;
+  int t = fast_div(item, p.r_mul, p.r_shr);
+  it.r = item - t * p.R;
+  const int t2 = fast_div(t, p.qp_mul, p.qp_shr);
+  const int qp = t - t2 * p.q_pairs;
+  t = t2;
   it.h = t % kHeads;
   it.b = t / kHeads;
   it.q0 = qp * 2 * kQTile;
   it.br = it.b * p.R + it.r;
-  int len = p.lengths ? p.lengths[it.b * p.ls_b + it.r * p.ls_r] : p.S;
   len = len < 0 ? 0 : (len > p.S ? p.S : len);
   it.uniform = len == 0 && p.empty_uniform;
   it.skip = len == 0 && !p.empty_uniform;
@@ -106,6 +123,9 @@ __device__ __forceinline__ Item decode_item(const AttnParams& p, int item) {
   it.nkt = (it.len + kKTile - 1) / kKTile;
   it.nvalid = (it.q0 + kQTile < p.S) ? 2 : 1;
   return it;
+}
+__device__ __forceinline__ Item decode_item(const AttnParams& p, int item) {
+  return decode_item(p, item, item_raw_length(p, item));
 }
 
 // Walks the (item, key tile) sequence of one CTA in order, skipping items without work.
@@ -202,10 +222,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   const int my_items = (p.num_items - 1 - int(blockIdx.x)) / int(gridDim.x) + 1;
 
-  // Register budget: the third warpgroup keeps 56 registers per thread and the two
-  // softmax warpgroups take 224 (128 x 56 + 256 x 224 = the whole register file).
+  // Register budget.  The CTA starts with 168 registers per thread; setmaxnreg only moves registers inside
+  // that allocation, and an increase blocks until a decrease has freed enough: the third warpgroup drops
+  // to 72 (frees 128 x 96) and the two softmax warpgroups rise to 216 (need 256 x 48, the same number).
   if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   }
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
@@ -263,8 +284,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // the loads is that a half's S buffer has been read out.
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kQTile, kKTile);                // Q·Kᵀ: both operands K-major
-      constexpr uint32_t idesc_b1 = make_idesc_bf16(kQTile, 128, false, true);     // I·Bias, one half: B MN-major
-      constexpr uint32_t idesc_b2 = make_idesc_bf16(kQTile, 256, false, true);     // I·[Bias0|Bias1], both halves
+      constexpr uint32_t idesc_b1 = make_idesc_bf16(kQTile, 128, false, true);     // I·Bias: B MN-major
       const uint32_t ti = tmem_base + kTmemI;
       const uint32_t d0 = tmem_base + kTmemS;  // S of half 0; half 1 follows 128 columns later
       int n0 = 0, n1 = 0;                      // S tiles issued per half (phase of S_FREE)
@@ -276,41 +296,35 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int ib = c.qi & 1, stage = c.g % kStages;
         if (c.kt == 0) ok = mbar_wait(bars + (Q_FULL + ib) * 8, (c.qi >> 1) & 1, abort_flag);
         ok = ok && mbar_wait(bars + (KB_FULL + stage) * 8, (c.g / kStages) & 1, abort_flag);
-        // the S buffers must have been read out by their warpgroups
-        ok = ok && mbar_wait(bars + (S_FREE + 0) * 8, (n0 & 1) ^ 1, abort_flag);
-        if (it.nvalid == 2) ok = ok && mbar_wait(bars + (S_FREE + 1) * 8, (n1 & 1) ^ 1, abort_flag);
         if (!ok) break;
-        tc_fence_after();
         // One descriptor per operand tile; the K steps only add a constant to its address field (in 16-byte
         // units), which keeps this single-thread issue path down to a few instructions per MMA.
         const uint32_t sbase = base + kSmStage + stage * kStageBytes;
         const uint64_t dk = make_smem_desc(sbase, 16, 512, kLayoutSw64);
         const uint64_t dq0 = make_smem_desc(base + kSmQ + ib * 16384, 16, 512, kLayoutSw64);
-        umma_ss(d0, dq0, dk, idesc_s, 0u);
-        umma_ss(d0, dq0 + 2, dk + 2, idesc_s, 1u);  // second 16 channels: +32 bytes
-        if (it.nvalid == 2) {
-          umma_ss(d0 + 128, dq0 + 512, dk, idesc_s, 0u);  // Q of half 1 lies 8 KiB further
-          umma_ss(d0 + 128, dq0 + 514, dk + 2, idesc_s, 1u);
-        }
-        if (!it.uniform) {
-          // Bias tiles: [128 query rows][64 keys] blocks with 128-byte swizzle, 16 KiB apart: keys 0-63 and
-          // 64-127 of half 0, then of half 1.  As B[key][query] this is MN-major with 16 query rows (2 KiB)
-          // per K step, so one N=256 MMA chain adds the bias of both halves (their S buffers are adjacent).
-          const uint64_t db = make_smem_desc(sbase + 8192, 16384, 1024, kLayoutSw128);
-          if (it.nvalid == 2) {
+        // Bias tiles: [128 query rows][64 keys] blocks with 128-byte swizzle, 16 KiB apart: keys 0-63 and
+        // 64-127 of half 0, then of half 1.  As B[key][query] this is MN-major with 16 query rows (2 KiB)
+        // per K step.
+        const uint64_t db0 = make_smem_desc(sbase + 8192, 16384, 1024, kLayoutSw128);
+        // The halves are issued separately, each as soon as its own S buffer has been read out, so the two
+        // softmax warpgroups need not run in step.
+        for (int w = 0; w < it.nvalid; ++w) {
+          ok = mbar_wait(bars + (S_FREE + w) * 8, ((w ? n1 : n0) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t d = d0 + w * 128;
+          const uint64_t dq = dq0 + w * 512;  // Q of half 1 lies 8 KiB further
+          umma_ss(d, dq, dk, idesc_s, 0u);
+          umma_ss(d, dq + 2, dk + 2, idesc_s, 1u);  // second 16 channels: +32 bytes
+          if (!it.uniform) {
+            const uint64_t db = db0 + w * 2048;  // bias of half 1 lies 32 KiB further
 #pragma unroll
-            for (int j = 0; j < 8; ++j) umma_ts(d0, ti + j * 8, db + j * 128, idesc_b2, 1u);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) umma_ts(d0, ti + j * 8, db + j * 128, idesc_b1, 1u);
+            for (int j = 0; j < 8; ++j) umma_ts(d, ti + j * 8, db + j * 128, idesc_b1, 1u);
           }
+          umma_commit(bars + (S_FULL + w) * 8);
+          if (w) ++n1; else ++n0;
         }
-        umma_commit(bars + (S_FULL + 0) * 8);
-        ++n0;
-        if (it.nvalid == 2) {
-          umma_commit(bars + (S_FULL + 1) * 8);
-          ++n1;
-        }
+        if (!ok) break;
         umma_commit(bars + (KB_EMPTY + stage) * 8);                      // K and bias are free once these MMAs ran
         if (c.kt == it.nkt - 1) umma_commit(bars + (Q_EMPTY + ib) * 8);  // last use of this item's Q
         cursor_next(p, c, my_items);
@@ -358,7 +372,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ softmax warpgroups
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int w = warp >> 2;               // which 128-query half
     const int m = (warp & 3) * 32 + lane;  // query row inside the half == TMEM lane
     const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
@@ -366,15 +380,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t o_addr = lane_taddr + kTmemO + w * 32;
     const uint32_t p_addr = lane_taddr + kTmemP + w * 64;
     const float c = p.scale_log2;                 // raw score -> log2-domain logit
-    const float raw_threshold = kRescaleThreshold / c;
     const uint64_t c2 = pack_f32x2(c, c);
     int ct = 0;  // tiles this half has processed (phase of S_FULL / O_FULL)
     bool ok = true;
-    Item nxt = decode_item(p, blockIdx.x);
+    int next_len = item_raw_length(p, blockIdx.x);
     for (int i = 0; ok && i < my_items; ++i) {
-      const Item it = nxt;
+      const Item it = decode_item(p, blockIdx.x + i * gridDim.x, next_len);
       // fetch the next item's row length now: its global-memory latency hides behind this item's work
-      if (i + 1 < my_items) nxt = decode_item(p, blockIdx.x + (i + 1) * gridDim.x);
+      if (i + 1 < my_items) next_len = item_raw_length(p, blockIdx.x + (i + 1) * gridDim.x);
       const int q = it.q0 + w * kQTile + m;  // query position
       __nv_bfloat16* out_row = p.out + it.br * p.o_br + (long long)q * p.o_s + it.h * p.o_h;
       if (it.skip) {
@@ -386,7 +399,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         continue;
       }
       if (w >= it.nvalid) continue;  // this half holds no query of the item
-      float row_max = -INFINITY, row_sum = 0.f;  // row_max in raw score units
+      float row_max = 0.f, row_sum = 0.f;  // row_max: reference point of the exponentials, in raw score units
       uint4 gv[4];                               // gate row, fetched during the last key tile
 #pragma unroll
       for (int j = 0; j < 4; ++j) gv[j] = make_uint4(0, 0, 0, 0);
@@ -421,25 +434,58 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           for (int j = 0; j < 128; ++j)
             if (j >= rem) s2[j] = -INFINITY;
         }
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
-#pragma unroll
-        for (int j = 0; j < 64; ++j) mx[j & 3] = max3_f32(mx[j & 3], s2[2 * j], s2[2 * j + 1]);
-        const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        // Lazy running max: the reference point of the exponentials only moves when the true max has
-        // grown by more than 2^8, so most tiles need no rescale of O.
-        float alpha = 1.f;
+        // The reference point of the exponentials is the maximum of the item's first key tile.  Later tiles
+        // skip the search for a maximum: fp32 sums, fp32 O and bf16 P share the fp32 exponent range, so
+        // probabilities far above 1 lose nothing, and a tile whose sum leaves the safe range is redone below.
         if (kt == 0) {
-          row_max = tile_max;
-        } else if (tile_max > row_max + raw_threshold) {
-          alpha = ex2_approx((row_max - tile_max) * c);
-          row_max = tile_max;
-        }
-        if (kt > 0) {
-          // the previous tile's P·V must be complete before P is overwritten and O rescaled
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
+#pragma unroll
+          for (int j = 0; j < 64; ++j) mx[j & 3] = max3_f32(mx[j & 3], s2[2 * j], s2[2 * j + 1]);
+          row_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));  // finite: key 0 of the first tile is valid
+        } else {
+          // the previous tile's P·V must be complete before P is overwritten
           ok = mbar_wait(bars + (O_FULL + w) * 8, (ct - 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+        }
+        // p = 2^(c * (s - row_max)); bf16 pairs go back to TMEM as the A operand of P·V
+        float tile_sum;
+        {
+          const float nmc = -row_max * c;
+          const uint64_t nmc2 = pack_f32x2(nmc, nmc);
+          uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};  // four independent packed partial sums
+#pragma unroll
+          for (int qtr = 0; qtr < 4; ++qtr) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const int j0 = qtr * 32 + 2 * e;
+              const uint64_t d2 = fma_f32x2(pack_f32x2(s2[j0], s2[j0 + 1]), c2, nmc2);
+              float d0, d1;
+              unpack_f32x2(d2, d0, d1);
+              const uint64_t p2 = pack_f32x2(ex2_approx(d0), ex2_approx(d1));
+              sum2[e & 3] = add_f32x2(sum2[e & 3], p2);
+              float p0, p1;
+              unpack_f32x2(p2, p0, p1);
+              pk[e] = pack_bf16x2(p0, p1);
+            }
+            tmem_st16(p_addr + qtr * 16, pk);
+          }
+          float a0, a1;
+          unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), a0, a1);
+          tile_sum = a0 + a1;
+        }
+        // Rare: some score lies so far above the reference point that the tile's sum leaves the safe range (or
+        // overflowed).  Move the reference point of the affected rows to the tile's maximum, rescale what has
+        // been accumulated (the previous P·V is complete, see above) and redo the tile.
+        if (__any_sync(0xffffffffu, !(tile_sum < kRebaseSum))) {
+          float cm = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 128; ++j) cm = fmaxf(cm, s2[j]);
+          const float new_max = (tile_sum < kRebaseSum) ? row_max : cm;
+          const float alpha = ex2_approx((row_max - new_max) * c);  // 1 for rows that keep their reference point
+          tmem_st_wait();
+          if (kt > 0) {
             uint32_t t[32];
             tmem_ld32(o_addr, t);
             tmem_ld_wait();
@@ -447,60 +493,48 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             for (int j = 0; j < 32; ++j) t[j] = __float_as_uint(__uint_as_float(t[j]) * alpha);
             tmem_st32(o_addr, t);
           }
-        }
-        // p = 2^(c * (s - row_max)); bf16 pairs go back to TMEM as the A operand of P·V
-        const float nmc = -row_max * c;
-        const uint64_t nmc2 = pack_f32x2(nmc, nmc);
-        uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};  // four independent packed partial sums
+          row_sum *= alpha;
+          row_max = new_max;
+          const float nmc = -row_max * c;
+          tile_sum = 0.f;
 #pragma unroll
-        for (int qtr = 0; qtr < 4; ++qtr) {
-          uint32_t pk[16];
+          for (int qtr = 0; qtr < 4; ++qtr) {
+            uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int j0 = qtr * 32 + 2 * e;
-            const uint64_t d2 = fma_f32x2(pack_f32x2(s2[j0], s2[j0 + 1]), c2, nmc2);
-            float d0, d1;
-            unpack_f32x2(d2, d0, d1);
-            const uint64_t p2 = pack_f32x2(ex2_approx(d0), ex2_approx(d1));
-            sum2[e & 3] = add_f32x2(sum2[e & 3], p2);
-            float p0, p1;
-            unpack_f32x2(p2, p0, p1);
-            pk[e] = pack_bf16x2(p0, p1);
+            for (int e = 0; e < 16; ++e) {
+              const int j0 = qtr * 32 + 2 * e;
+              const float p0 = ex2_approx(fmaf(s2[j0], c, nmc)), p1 = ex2_approx(fmaf(s2[j0 + 1], c, nmc));
+              tile_sum += p0 + p1;
+              pk[e] = pack_bf16x2(p0, p1);
+            }
+            tmem_st16(p_addr + qtr * 16, pk);
           }
-          tmem_st16(p_addr + qtr * 16, pk);
         }
-        {
-          float a0, a1;
-          unpack_f32x2(add_f32x2(add_f32x2(sum2[0], sum2[1]), add_f32x2(sum2[2], sum2[3])), a0, a1);
-          row_sum = fmaf(row_sum, alpha, a0 + a1);
-        }
+        row_sum += tile_sum;
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + (P_FULL + w) * 8);
       }
       if (!ok) break;
-      // Gate factors first: they only need the gate row fetched during the last tile, and computing them here
-      // fills the time the last P·V takes.
+      // Output factors first (gate / row sum): they only need the gate row fetched during the last tile, and
+      // computing them here fills the time the last P·V takes.
       float sg[32];
+      const float inv = 1.f / row_sum;
       if (p.gate != nullptr) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const uint32_t gw[4] = {gv[j].x, gv[j].y, gv[j].z, gv[j].w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            // sigmoid(x) = 0.5 * tanh(x / 2) + 0.5
-            sg[j * 8 + 2 * e] = fmaf(0.5f, tanh_approx(0.5f * bf16_lo(gw[e])), 0.5f);
-            sg[j * 8 + 2 * e + 1] = fmaf(0.5f, tanh_approx(0.5f * bf16_hi(gw[e])), 0.5f);
+            sg[j * 8 + 2 * e] = bf16_lo(gw[e]) * inv;
+            sg[j * 8 + 2 * e + 1] = bf16_hi(gw[e]) * inv;
           }
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) sg[j] = 1.f;
+        for (int j = 0; j < 32; ++j) sg[j] = inv;
       }
-      const float inv = 1.f / row_sum;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) sg[j] *= inv;
       // the item's output: O (in TMEM) / row_sum * gate
       ok = mbar_wait(bars + (O_FULL + w) * 8, (ct - 1) & 1, abort_flag);
       if (!ok) break;
@@ -536,6 +570,23 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (threadIdx.x == 0 && *abort_flag) *p.status = B200TA_ERR_DEVICE_WAIT;
 }
 
+}  // namespace
+}  // namespace b200ta
+
+namespace b200ta {
+namespace {
+// Constants for fast_div: with l = ceil(log2 d) and mul = floor(2^(31+l) / d) + 1, floor(n / d) equals
+// (n * mul) >> (31 + l) for every n < 2^31.
+void fast_div_constants(uint32_t d, uint32_t* mul, uint32_t* shr) {
+  if (d <= 1) {
+    *mul = 0, *shr = 0;
+    return;
+  }
+  uint32_t l = 0;
+  while ((uint64_t(1) << l) < d) ++l;
+  *mul = uint32_t((uint64_t(1) << (31 + l)) / d + 1);
+  *shr = l - 1;
+}
 }  // namespace
 }  // namespace b200ta
 
@@ -587,6 +638,8 @@ int b200ta_attention(const void* q, const void* k, const void* v, const void* ga
   p.B = B, p.R = R, p.S = S, p.S_pad = S_pad;
   p.q_pairs = int(q_pairs);
   p.num_items = int(items);
+  fast_div_constants(uint32_t(R), &p.r_mul, &p.r_shr);
+  fast_div_constants(uint32_t(q_pairs), &p.qp_mul, &p.qp_shr);
   p.lengths = lengths;
   p.ls_b = ls_b, p.ls_r = ls_r;
   p.gate = static_cast<const __nv_bfloat16*>(gate);

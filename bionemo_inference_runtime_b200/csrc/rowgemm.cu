@@ -268,6 +268,15 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                              o0, o1);
                 packed[j] = pack_bf16x2(o0, o1);
               }
+              if (n0 >= 3 * kC) {
+                // Gate plane: store sigmoid(g), computed from the bf16-rounded logit and rounded to bf16 again
+                // as the eager bf16 module does (gate.sigmoid_() on a bf16 tensor).  The attention kernel then
+                // only multiplies.  sigmoid(x) = 0.5 * tanh(x / 2) + 0.5.
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  packed[j] = pack_bf16x2(fmaf(0.5f, tanh_approx(0.5f * bf16_lo(packed[j])), 0.5f),
+                                          fmaf(0.5f, tanh_approx(0.5f * bf16_hi(packed[j])), 0.5f));
+              }
               if (s < p.S) {
                 // head-major planes: 64 contiguous bytes per (plane, head, position)
                 __nv_bfloat16* dst = p.out + (n0 >> 7) * p.qs_which + (long long)br * p.qs_br + ((n0 >> 5) & 3) * p.qs_h +

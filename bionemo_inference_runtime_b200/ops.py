@@ -92,9 +92,9 @@ def prologue(z, packed, eps: float = 1e-5, *, ending: bool = False, want_qkvg: b
              want_bias: bool = True, transposed_bias: bool = False):
     """LayerNorm + q/k/v/g projection + triangle-bias projection.
 
-    Returns ``(qkvg, bias)``: ``qkvg`` is ``[4, B*R, H, S, D]`` (q, k, v, g planes, head-major),
-    ``bias`` is ``[B, H, S_q, S_pad]`` scaled by log2(e).  With ``ending`` the rows R run over
-    the second pair axis of ``z``.
+    Returns ``(qkvg, bias)``: ``qkvg`` is ``[4, B*R, H, S, D]`` (q, k, v, g planes, head-major; the g plane
+    holds ``sigmoid(gate logit)``), ``bias`` is ``[B, H, S_q, S_pad]`` multiplied by ``BIAS_SCALE``
+    (divided by the softmax scale).  With ``ending`` the rows R run over the second pair axis of ``z``.
     """
     _require_cuda_bf16("z", z)
     B, R, S, sb, sr, ss = _pair_strides(z, ending)
@@ -126,7 +126,11 @@ def prologue(z, packed, eps: float = 1e-5, *, ending: bool = False, want_qkvg: b
 def attention(qkvg: torch.Tensor, bias: torch.Tensor, lengths: torch.Tensor | None, B: int, R: int, S: int, *,
               gate: bool = True, out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
               empty_row_mode: int = _lib.EMPTY_ROW_UNIFORM, scale: float | None = None) -> torch.Tensor:
-    """Biased, length-masked attention over the head-major ``qkvg`` planes; returns ``[B, R, S, 128]``."""
+    """Biased, length-masked attention over the head-major ``qkvg`` planes; returns ``[B, R, S, 128]``.
+
+    ``bias`` is the triangle bias times ``BIAS_SCALE`` and, with ``gate``, the g plane holds gate factors in
+    [0, 1] (sigmoid already applied) - the forms ``prologue`` writes.
+    """
     _require_cuda_bf16("qkvg", qkvg)
     _require_cuda_bf16("bias", bias)
     if out is None:

@@ -103,6 +103,9 @@ int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const voi
  *   z          [B,R,S,128] via element strides (zs_b, zs_r, zs_s); channel stride 1.
  *   qkvg       output, four planes (q,k,v,g) of [B*R, 4 heads, S, 32]:
  *              element (which, br, h, s, d) at which*qs_which + br*qs_br + h*qs_h + s*qs_s + d.
+ *              The g plane holds sigmoid(gate logit), rounded to bf16 from the bf16-rounded logit as
+ *              the eager module's gate.sigmoid_() does (bionemo_ir/_torch/layers/attention.py:288);
+ *              it is the `gate` operand of b200ta_attention.
  *   bias       output, bias[b,h,q=r,k=s] * sqrt(32) (i.e. divided by the softmax scale, the form
  *              b200ta_attention consumes) at b*bs_b + h*bs_h + r*bs_q + s*bs_k;
  *              entries S <= s < S_pad are written as zero.  May be NULL (no bias written).
@@ -120,7 +123,8 @@ int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
 /*
  * Attention core.  For every (b, r, h) and query s:
  *   o[s,:] = softmax_t( scale * (q[s]·k[t] + bias[b,h,s,t]) ; t < len[b,r] ) · v[t,:]
- * optionally multiplied by sigmoid(gate) in the epilogue.
+ * optionally multiplied by gate[s,:], the gate factors in [0,1] (sigmoid already applied, as
+ * b200ta_prologue writes them).
  *
  *   q,k,v,gate [B*R, 4, S, 32] via element strides (br, h, s); d stride 1; gate may be NULL.
  *   bias       [B, 4, S, S_pad]: the additive triangle bias DIVIDED by softmax_scale (the tensor core adds
@@ -134,7 +138,7 @@ int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
  *
  * Replaces: triangle_attention.launch(config, LaunchParams)
  * (cpp/kernels/cutedsl_triangle_attention/launcher.h:515-532, launcher.cpp:548-627) and the
- * sigmoid gate of bionemo_ir/_torch/layers/attention.py:285-287.
+ * gate multiply of bionemo_ir/_torch/layers/attention.py:285-288.
  */
 int b200ta_attention(const void* q, const void* k, const void* v, const void* gate, int64_t s_br,
                      int64_t s_h, int64_t s_s, const void* bias, int64_t bs_b, int64_t bs_h,

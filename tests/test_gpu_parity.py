@@ -233,6 +233,32 @@ def test_empty_rows_zeros_mode_and_lengths_beyond_every_boundary():
             assert (out.cpu().view(B * R, S, 128)[~valid] == 0).all()
 
 
+def test_scores_far_above_the_first_key_tile_move_the_reference_point():
+    """The softmax is anchored at the maximum of a row's first key tile; keys ~180 nats above it (and, in one
+    row, back below it) must move that reference point without losing the earlier tiles' contribution."""
+    torch.manual_seed(61)
+    B, R, S = 1, 3, 512
+    for jump_at in (128, 200):
+        qkvg = torch.randn(4, B * R, 4, S, 32) * 0.1
+        qkvg[0] += 4.0
+        qkvg[1, :, :, :jump_at] -= 4.0
+        qkvg[1, :, :, jump_at:] += 4.0
+        qkvg[1, 1, :, 300:] -= 8.0
+        qkvg[2] = torch.randn(B * R, 4, S, 32)
+        qkvg[3] = torch.rand(B * R, 4, S, 32)  # gate factors in [0, 1]
+        qkvg = qkvg.bfloat16()
+        bias = torch.randn(B, 4, S, S).bfloat16()
+        q, k, v, g = [t.float().permute(0, 2, 1, 3) for t in qkvg]  # [BR, S, H, d]
+        want, want_lse = orc.attention_core(q, k, v, bias.float(), torch.full((B * R,), S, dtype=torch.int32),
+                                            1 / math.sqrt(32))
+        lse = torch.full((B * R, S, 4), float("nan"), device=DEV)
+        out = ops.attention(qkvg.to(DEV), (bias.float() * ops.BIAS_SCALE).bfloat16().to(DEV), None, B, R, S,
+                            gate=True, lse=lse)
+        assert _lib.device_status() == 0
+        torch.testing.assert_close(out.float().cpu().view(B * R, S, 4, 32), want * g, rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(lse.cpu(), want_lse, rtol=1e-3, atol=5e-2)
+
+
 def test_backend_forward_on_packed_views():
     """q, k, v as views of one in-projection buffer, as the reference layer hands them to a backend."""
     torch.manual_seed(7)
