@@ -235,18 +235,37 @@ def run_ours(args) -> dict:
         raise RuntimeError("a kernel abandoned a bounded wait during the benchmark")
 
     # ---- end to end: pinned host -> device -> step -> pinned host ----------------------------------------
+    # Through the package's HostPipeline: every step copies its 64 MiB input in and its result out; the copies
+    # of neighbouring steps overlap the compute on separate streams (two device slots, two buffer sets).
     z_pin = z_host.pin_memory()
-    out_pin = torch.empty_like(z_pin).pin_memory()
-    e2e_times = []
-    for i in range(3 + args.steps):
+    outs_pin = [torch.empty_like(z_pin).pin_memory() for _ in range(2)]
+    slot_bufs: list[dict] = [{}, {}]
+
+    def slot_step(zd, slot):
+        z1 = start(zd, mask_bias=pre.mask_bias, buffers=slot_bufs[slot], residual=True)
+        z2 = end(z1, mask_bias=pre.mask_bias_transposed, buffers=slot_bufs[slot], residual=True, inplace_residual=True)
+        if cfg["transition"]:
+            z2 = trans(z2, residual=True, inplace=True)
+        return z2
+
+    pipe = b200.HostPipeline(slot_step, z_pin, device, depth=2)
+    pipe.run([z_pin] * 4, [outs_pin[i & 1] for i in range(4)])  # warm-up
+    barrier()
+    t0 = time.perf_counter()
+    pipe.run([z_pin] * args.steps, [outs_pin[i & 1] for i in range(args.steps)])
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    # the same path one step at a time (latency of a single pair tensor: copy in, compute, copy out)
+    serial = []
+    for i in range(3 + min(args.steps, 20)):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        zd = z_pin.to(device, non_blocking=True)
-        out_pin.copy_(step(zd), non_blocking=True)
-        torch.cuda.synchronize()
+        pipe.run([z_pin], [outs_pin[0]])
         if i >= 3:
-            e2e_times.append((time.perf_counter() - t0) * 1e3)
-    e2e_ms = sum(e2e_times) / len(e2e_times)
+            serial.append((time.perf_counter() - t0) * 1e3)
+    e2e_serial_ms = sum(serial) / len(serial)
+    if not torch.equal(outs_pin[0], outs_pin[1]):
+        raise RuntimeError("pipelined end-to-end outputs differ between slots")
 
     # ---- per-kernel timing of the dominant kernel (attention core), live, with CUDA events ------------------
     B, N = cfg["B"], cfg["N"]
@@ -285,7 +304,9 @@ def run_ours(args) -> dict:
                    "valid_lengths": cfg["valid"], "l2": "flushed between timed steps (256 MiB write)",
                    "empty_row_mode": "uniform", "parallelism": f"independent batches x{world}"},
         "e2e": {"value": flops_all / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": bytes_io, "d2h_bytes_per_step": bytes_io},
+                "h2d_bytes_per_step": bytes_io, "d2h_bytes_per_step": bytes_io,
+                "mode": "HostPipeline depth 2: copies of neighbouring steps overlap the compute",
+                "single_step_latency_ms": e2e_serial_ms},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"kernel": "attention_kernel", "bound": "tensor", "achieved": attn_flops / attn_ms / 1e9,
                      "peak": peak_tf, "unit": "TFLOP/s", "frac": attn_flops / attn_ms / 1e9 / peak_tf,
