@@ -62,12 +62,13 @@ class KernelStages:
 
 
 def shard(z: torch.Tensor, rank: int, world: int, layout: str = ROWS) -> torch.Tensor:
-    """The contiguous local shard of a full pair tensor (for tests and for loading inputs)."""
+    """A contiguous copy of the local shard of a full pair tensor (for tests and for loading inputs); never a view
+    of ``z``, because the sharded block updates its shard in place."""
     n = z.shape[1] // world
     if z.shape[1] % world or z.shape[1] != z.shape[2]:
         raise ValueError(f"need a square pair tensor whose side is divisible by the world size, got {tuple(z.shape)}")
     part = z[:, rank * n:(rank + 1) * n] if layout == ROWS else z[:, :, rank * n:(rank + 1) * n]
-    return part.contiguous()
+    return part.clone(memory_format=torch.contiguous_format)
 
 
 def exchange(x: torch.Tensor, to_layout: str, group=None) -> torch.Tensor:
