@@ -40,6 +40,7 @@ struct RowGemmParams {
   long long os_b, os_r, os_s;                 // epilogue strides (elements)
   int want_qkvg;
   int has_residual;
+  int wide_store;  // output base 32-byte aligned and every stride a multiple of 16 elements
   int* status;
 };
 
@@ -63,6 +64,23 @@ enum Bar { W_FULL = 0, A_FULL = 1, A_EMPTY = 3, ACC_FULL = 5, ACC_EMPTY = 7, NUM
 
 __device__ __forceinline__ void stg128(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   *reinterpret_cast<uint4*>(p) = make_uint4(a, b, c, d);
+}
+// 32-byte store (one full sector per lane); the address must be 32-byte aligned.
+__device__ __forceinline__ void stg256(void* p, const uint32_t* v) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+               "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+
+// 64 contiguous bytes of one output row: two 32-byte stores when base and strides allow, else four of 16.
+__device__ __forceinline__ void store_row64(__nv_bfloat16* dst, const uint32_t (&v)[16], bool wide) {
+  if (wide) {
+    stg256(dst, v);
+    stg256(dst + 16, v + 8);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) stg128(dst + c * 8, v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+  }
 }
 
 template <int MODE>
@@ -250,19 +268,28 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
           }
         } else {
-          const int ngroups = MODE == kPrologue ? 8 : 4;
-          for (int g = e; g < ngroups; g += 2) {
-            uint32_t a[32];
-            tmem_ld32(acc_addr + g * 32, a);
+          // This warpgroup takes the 32-column groups e, e+2, ...  The TMEM load of the next group is issued
+          // before the current group's math, and the per-column constants are fetched from shared memory
+          // before the wait for the current load, so neither latency is exposed.
+          constexpr int kGroupsPerWg = MODE == kPrologue ? 4 : 2;
+          uint32_t acc[2][32];
+          tmem_ld32(acc_addr + e * 32, acc[0]);
+#pragma unroll
+          for (int gi = 0; gi < kGroupsPerWg; ++gi) {
+            const int g = e + 2 * gi;
             const int n0 = (MODE == kPrologue ? u * 256 : 0) + g * 32;
+            uint32_t (&a)[32] = acc[gi & 1];
             uint32_t packed[16];
             if (MODE == kPrologue) {
+              float4 t[16];  // {rowsum0, rowsum1, const0, const1} of columns n0+2j, n0+2j+1
               const float4* sc4 = reinterpret_cast<const float4*>(gen + L::kVec) + (n0 >> 1);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) t[j] = sc4[j];
               tmem_ld_wait();
+              if (gi + 1 < kGroupsPerWg) tmem_ld32(acc_addr + (g + 2) * 32, acc[(gi + 1) & 1]);
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const float4 t = sc4[j];  // {rowsum0, rowsum1, const0, const1} of columns n0+2j, n0+2j+1
-                const uint64_t off = fma_f32x2(nmr2, pack_f32x2(t.x, t.y), pack_f32x2(t.z, t.w));
+                const uint64_t off = fma_f32x2(nmr2, pack_f32x2(t[j].x, t[j].y), pack_f32x2(t[j].z, t[j].w));
                 float o0, o1;
                 unpack_f32x2(fma_f32x2(rstd2, pack_f32x2(__uint_as_float(a[2 * j]), __uint_as_float(a[2 * j + 1])), off),
                              o0, o1);
@@ -281,9 +308,7 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 // head-major planes: 64 contiguous bytes per (plane, head, position)
                 __nv_bfloat16* dst = p.out + (n0 >> 7) * p.qs_which + (long long)br * p.qs_br + ((n0 >> 5) & 3) * p.qs_h +
                                      (long long)s * p.qs_s;
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                  stg128(dst + c * 8, packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+                store_row64(dst, packed, p.wide_store != 0);
               }
             } else {
               const float* bo = reinterpret_cast<const float*>(gen + L::kVec) + n0;
@@ -299,18 +324,23 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 16; ++j) res[j] = 0u;
               }
+              float bov[32];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 t = reinterpret_cast<const float4*>(bo)[j];
+                bov[4 * j] = t.x, bov[4 * j + 1] = t.y, bov[4 * j + 2] = t.z, bov[4 * j + 3] = t.w;
+              }
               tmem_ld_wait();
+              if (gi + 1 < kGroupsPerWg) tmem_ld32(acc_addr + (g + 2) * 32, acc[(gi + 1) & 1]);
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const float o0 = __uint_as_float(a[2 * j]) + bo[2 * j] + bf16_lo(res[j]);
-                const float o1 = __uint_as_float(a[2 * j + 1]) + bo[2 * j + 1] + bf16_hi(res[j]);
+                const float o0 = __uint_as_float(a[2 * j]) + bov[2 * j] + bf16_lo(res[j]);
+                const float o1 = __uint_as_float(a[2 * j + 1]) + bov[2 * j + 1] + bf16_hi(res[j]);
                 packed[j] = pack_bf16x2(o0, o1);
               }
               if (s < p.S) {
                 __nv_bfloat16* dst = p.out + b * p.os_b + r * p.os_r + (long long)s * p.os_s + n0;
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                  stg128(dst + c * 8, packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+                store_row64(dst, packed, p.wide_store != 0);
               }
             }
           }
@@ -404,6 +434,8 @@ int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
   p.out = static_cast<__nv_bfloat16*>(qkvg);
   p.qs_which = qs_which, p.qs_br = qs_br, p.qs_h = qs_h, p.qs_s = qs_s;
   p.want_qkvg = want_qkvg ? 1 : 0;
+  p.wide_store = (reinterpret_cast<uintptr_t>(qkvg) & 31u) == 0 && qs_which % 16 == 0 && qs_br % 16 == 0 &&
+                 qs_h % 16 == 0 && qs_s % 16 == 0;
   p.status = st->status_dev;
 
   auto kern = rowgemm_kernel<kPrologue>;
@@ -457,6 +489,7 @@ int b200ta_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, co
   p.out = static_cast<__nv_bfloat16*>(out);
   p.os_b = os_b, p.os_r = os_r, p.os_s = os_s;
   p.has_residual = residual ? 1 : 0;
+  p.wide_store = (reinterpret_cast<uintptr_t>(out) & 31u) == 0 && os_b % 16 == 0 && os_r % 16 == 0 && os_s % 16 == 0;
   p.status = st->status_dev;
 
   auto kern = rowgemm_kernel<kEpilogue>;
