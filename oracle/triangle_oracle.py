@@ -242,3 +242,94 @@ def transition_forward(x: torch.Tensor, mask: torch.Tensor | None, w: Transition
         m = mask if mask.dim() == y.dim() else mask.unsqueeze(-1)
         y = y * m.to(dtype)
     return xd + y if residual else y
+
+
+# ------------------------------------------------------------------------------------------ triangle multiplication
+
+OUTGOING = 0
+INCOMING = 1
+
+
+@dataclass
+class TriMulWeights:
+    """Parameters of one triangle-multiplication node, named as in the reference state_dict."""
+
+    ln_in_w: torch.Tensor  # norm_in.weight [c]
+    ln_in_b: torch.Tensor  # norm_in.bias [c]
+    w_p_in: torch.Tensor  # p_in.weight [2*hidden, c]: a rows, then b rows
+    w_g_in: torch.Tensor  # g_in.weight [2*hidden, c]
+    ln_out_w: torch.Tensor  # norm_out.weight [hidden]
+    ln_out_b: torch.Tensor  # norm_out.bias [hidden]
+    w_p_out: torch.Tensor  # p_out.weight [c, hidden]
+    w_g_out: torch.Tensor  # g_out.weight [c, c]
+    b_p_in: torch.Tensor | None = None
+    b_g_in: torch.Tensor | None = None
+    b_p_out: torch.Tensor | None = None
+    b_g_out: torch.Tensor | None = None
+
+    def fields(self):
+        return (self.ln_in_w, self.ln_in_b, self.w_p_in, self.w_g_in, self.ln_out_w, self.ln_out_b, self.w_p_out,
+                self.w_g_out, self.b_p_in, self.b_g_in, self.b_p_out, self.b_g_out)
+
+    def to(self, dtype: torch.dtype) -> "TriMulWeights":
+        return TriMulWeights(*[None if t is None else t.to(dtype) for t in self.fields()])
+
+
+def make_trimul_weights(seed: int, c: int = 128, hidden: int = 128, std: float = 0.02, identity_ln: bool = True,
+                        biases: bool = False) -> TriMulWeights:
+    """Seeded weights in the recipe of ``init_module_weights`` (tests/_torch/__init__.py:33-63)."""
+    g = torch.Generator().manual_seed(seed)
+    w_p_in = torch.randn(2 * hidden, c, generator=g) * std
+    w_g_in = torch.randn(2 * hidden, c, generator=g) * std
+    w_p_out = torch.randn(c, hidden, generator=g) * std
+    w_g_out = torch.randn(c, c, generator=g) * std
+    if identity_ln:
+        ln = [torch.ones(c), torch.zeros(c), torch.ones(hidden), torch.zeros(hidden)]
+    else:
+        ln = [1 + 0.2 * torch.randn(c, generator=g), 0.2 * torch.randn(c, generator=g),
+              1 + 0.2 * torch.randn(hidden, generator=g), 0.2 * torch.randn(hidden, generator=g)]
+    bs = [None] * 4
+    if biases:
+        bs = [0.1 * torch.randn(n, generator=g) for n in (2 * hidden, 2 * hidden, c, c)]
+    return TriMulWeights(ln[0], ln[1], w_p_in, w_g_in, ln[2], ln[3], w_p_out, w_g_out, *bs)
+
+
+def trimul_stages(z: torch.Tensor, mask: torch.Tensor | None, w: TriMulWeights, direction: int = OUTGOING,
+                  eps: float = 1e-5, mean_normalization: bool = False) -> dict:
+    """Every intermediate of one triangle-multiplication node.
+
+    Reference: TriangleMultiplicationNode._forward_impl (bionemo_ir/_torch/layers/triangle_nodes.py:646-727),
+    the unfused dual GEMMs (bionemo_ir/_torch/custom_ops/dual_gemm_x_x/ops.py:34-58,
+    dual_gemm_x0_x1/ops.py:29-52), _contract_projection (triangle_nodes.py:596-612) and the tests' mirror
+    RefTriangleMultiplicationNode.forward (tests/common/test_utils/boltz/ref_layers.py:59-96).
+    """
+    dtype = w.ln_in_w.dtype
+    x = z.to(dtype)
+    B, I, J, c = x.shape
+    if mask is None:
+        mask = x.new_ones(B, I, J)
+    mask = mask.to(dtype)
+    x_in = F.layer_norm(x, (c,), w.ln_in_w, w.ln_in_b, eps)
+    ab = torch.sigmoid(F.linear(x_in, w.w_g_in, w.b_g_in)) * F.linear(x_in, w.w_p_in, w.b_p_in)
+    ab = ab * mask.unsqueeze(-1)
+    a, b = torch.chunk(ab, 2, dim=-1)
+    if mean_normalization:
+        n_valid = mask[:, 0, :].sum(dim=-1)
+        b = b / (n_valid[:, None, None, None] + 1e-3)
+    if direction == OUTGOING:
+        t = torch.einsum("bikd,bjkd->bijd", a, b)
+    else:
+        t = torch.einsum("bkid,bkjd->bijd", a, b)
+    hidden = t.shape[-1]
+    normed = F.layer_norm(t.to(w.ln_out_w.dtype), (hidden,), w.ln_out_w, w.ln_out_b, eps)
+    hp = w.w_p_out.dtype
+    update = torch.sigmoid(F.linear(x_in.to(hp), w.w_g_out, w.b_g_out)) * F.linear(normed.to(hp), w.w_p_out, w.b_p_out)
+    return {"x_in": x_in, "ab": ab, "a": a, "b": b, "contracted": t, "normed": normed, "update": update}
+
+
+def trimul_forward(z: torch.Tensor, mask: torch.Tensor | None, w: TriMulWeights, direction: int = OUTGOING, *,
+                   residual: bool = False, **kw) -> torch.Tensor:
+    """Output of the node [B, I, J, c]: the update, or ``z + update`` with ``residual``
+    (triangle_nodes.py:723-727: the unfused path adds the residual without masking it)."""
+    st = trimul_stages(z, mask, w, direction, **kw)
+    return z.to(st["update"].dtype) + st["update"] if residual else st["update"]

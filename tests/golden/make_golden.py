@@ -166,6 +166,59 @@ def main() -> None:
     save("transition", x=x, mask=tmask, out_residual_masked=ref_res, out_update=ref_upd, out_module_update_masked=mod_upd,
          out_module_update_masked_bf16=mod_upd16, **{f"w_{k}": v for k, v in tw.items()})
 
+    trimul_cases()
+
+
+def trimul_cases() -> None:
+    """Triangle multiplication.  The reference module itself needs CUDA to construct (it probes the SM version and
+    its LayerNorm-transpose op takes CUDA tensors only), so the fixtures come from (i) the pure-PyTorch mirror the
+    reference's own tests compare against, RefTriangleMultiplicationNode (tests/common/test_utils/boltz/ref_layers.py),
+    and (ii) the reference's unfused dual-GEMM functions chained exactly as TriangleMultiplicationNode._forward_impl
+    chains them (bf16 run, including the mean-normalised variant)."""
+    sys.path.insert(0, str(REF / "tests" / "common"))
+    from test_utils.boltz.ref_layers import RefTriangleMultiplicationNode
+    from bionemo_ir._torch.custom_ops.dual_gemm_x0_x1.ops import _invoke_vanilla_dual_gemm_x0_x1
+    from bionemo_ir._torch.custom_ops.dual_gemm_x_x.ops import _invoke_vanilla_dual_gemm_x_x
+
+    g = torch.Generator().manual_seed(1003)
+    N = 20
+    z = torch.randn(2, N, N, 128, generator=g).bfloat16().float()
+    m = torch.zeros(2, N)
+    m[0, :13] = 1
+    m[1, :N] = 1
+    mask = m[:, :, None] * m[:, None, :]
+    w = {
+        "ln_in_w": 1 + 0.2 * torch.randn(128, generator=g), "ln_in_b": 0.2 * torch.randn(128, generator=g),
+        "w_p_in": torch.randn(256, 128, generator=g) * 0.02, "w_g_in": torch.randn(256, 128, generator=g) * 0.02,
+        "ln_out_w": 1 + 0.2 * torch.randn(128, generator=g), "ln_out_b": 0.2 * torch.randn(128, generator=g),
+        "w_p_out": torch.randn(128, 128, generator=g) * 0.02, "w_g_out": torch.randn(128, 128, generator=g) * 0.02,
+    }
+    w = {k: v.bfloat16().float() for k, v in w.items()}
+    outs = {}
+    for name, outgoing in (("outgoing", True), ("incoming", False)):
+        ref = RefTriangleMultiplicationNode(128, outgoing=outgoing)
+        ref.norm_in.weight.data.copy_(w["ln_in_w"]), ref.norm_in.bias.data.copy_(w["ln_in_b"])
+        ref.norm_out.weight.data.copy_(w["ln_out_w"]), ref.norm_out.bias.data.copy_(w["ln_out_b"])
+        ref.p_in.weight.data.copy_(w["w_p_in"]), ref.g_in.weight.data.copy_(w["w_g_in"])
+        ref.p_out.weight.data.copy_(w["w_p_out"]), ref.g_out.weight.data.copy_(w["w_g_out"])
+        outs[f"update_{name}"] = ref(z, mask)
+
+        # the module's own chain of unfused ops in bf16 (high_precision=False): triangle_nodes.py:680-722
+        wb = {k: v.bfloat16() for k, v in w.items()}
+        x_in = torch.nn.functional.layer_norm(z.bfloat16(), (128,), wb["ln_in_w"], wb["ln_in_b"], 1e-5)
+        for mean_norm in (False, True):
+            proj = _invoke_vanilla_dual_gemm_x_x(x_in, wb["w_g_in"], wb["w_p_in"], None, None, mask.bfloat16(),
+                                                 transpose_out=True)
+            a, b = torch.chunk(proj, 2, dim=0)
+            if mean_norm:
+                n_valid = mask.bfloat16()[:, 0, :].sum(dim=-1)
+                b = b / (n_valid[None, :, None, None] + 1e-3)
+            t = torch.einsum("dbik,dbjk->dbij", a, b) if outgoing else torch.einsum("dbki,dbkj->dbij", a, b)
+            t = torch.nn.functional.layer_norm(t.permute(1, 2, 3, 0), (128,), wb["ln_out_w"], wb["ln_out_b"], 1e-5)
+            upd = _invoke_vanilla_dual_gemm_x0_x1(x_in, t, wb["w_g_out"], wb["w_p_out"])
+            outs[f"update_{name}_bf16{'_meannorm' if mean_norm else ''}"] = upd
+    save("trimul", z=z, mask=mask, **outs, **{f"w_{k}": v for k, v in w.items()})
+
 
 if __name__ == "__main__":
     with torch.no_grad():

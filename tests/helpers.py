@@ -27,3 +27,8 @@ def golden_node_weights(g: dict, dtype=torch.float32) -> orc.NodeWeights:
 
 def golden_transition_weights(g: dict, dtype=torch.float32) -> orc.TransitionWeights:
     return orc.TransitionWeights(g["w_ln_w"], g["w_ln_b"], g["w_w1"], g["w_w2"]).to(dtype)
+
+
+def golden_trimul_weights(g: dict, dtype=torch.float32) -> orc.TriMulWeights:
+    return orc.TriMulWeights(g["w_ln_in_w"], g["w_ln_in_b"], g["w_w_p_in"], g["w_w_g_in"], g["w_ln_out_w"],
+                             g["w_ln_out_b"], g["w_w_p_out"], g["w_w_g_out"]).to(dtype)

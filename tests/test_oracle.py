@@ -1,9 +1,10 @@
 """Pins the CPU oracle against outputs of the reference's own modules (tests/golden/*.npz)."""
 
+import pytest
 import torch
 
 from oracle import triangle_oracle as orc
-from tests.helpers import golden_node_weights, golden_transition_weights, load_golden
+from tests.helpers import golden_node_weights, golden_transition_weights, golden_trimul_weights, load_golden
 
 
 def test_start_node_full_mask_fp32():
@@ -77,3 +78,24 @@ def test_transition_bf16_matches_eager_rounding():
     w = golden_transition_weights(g, torch.bfloat16)
     mod = orc.transition_forward(g["x"].bfloat16(), g["mask"].bfloat16(), w)
     assert (mod.float() - g["out_module_update_masked_bf16"]).abs().max() <= 2 ** -8
+
+
+@pytest.mark.parametrize("name,direction", [("outgoing", orc.OUTGOING), ("incoming", orc.INCOMING)])
+def test_triangle_multiplication_fp32_matches_the_reference_tests_mirror(name, direction):
+    g = load_golden("trimul")
+    w = golden_trimul_weights(g)
+    upd = orc.trimul_forward(g["z"], g["mask"], w, direction)
+    assert (upd - g[f"update_{name}"]).abs().max() < 2e-6
+    res = orc.trimul_forward(g["z"], g["mask"], w, direction, residual=True)
+    assert (res - (g["z"] + g[f"update_{name}"])).abs().max() < 2e-6
+
+
+@pytest.mark.parametrize("name,direction", [("outgoing", orc.OUTGOING), ("incoming", orc.INCOMING)])
+@pytest.mark.parametrize("mean_norm", [False, True])
+def test_triangle_multiplication_bf16_matches_the_unfused_reference_ops(name, direction, mean_norm):
+    g = load_golden("trimul")
+    w = golden_trimul_weights(g, torch.bfloat16)
+    upd = orc.trimul_forward(g["z"].bfloat16(), g["mask"].bfloat16(), w, direction, mean_normalization=mean_norm)
+    want = g[f"update_{name}_bf16{'_meannorm' if mean_norm else ''}"]
+    # same ops in the same order; einsum summation order may differ by an ulp of the bf16 contraction result
+    assert (upd.float() - want).abs().max() <= 2 ** -7 * max(1.0, want.abs().max().item())
