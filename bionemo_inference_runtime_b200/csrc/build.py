@@ -19,7 +19,8 @@ CSRC = Path(__file__).resolve().parent
 PKG = CSRC.parent
 LIB = PKG / "libb200ta.so"
 OBJ_DIR = CSRC / "build"
-SOURCES = ["host.cu", "pack.cu", "rowgemm.cu", "attention.cu", "node.cu", "transition.cu"]
+SOURCES = ["host.cu", "pack.cu", "rowgemm.cu", "attention.cu", "node.cu", "transition.cu", "trimul_project.cu",
+           "trimul_contract.cu", "trimul_output.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--use_fast_math",

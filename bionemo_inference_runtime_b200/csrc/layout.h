@@ -29,4 +29,15 @@ constexpr size_t kTransW2Off = kTransScOff + size_t(kTransRows) * 8;      // bf1
 constexpr size_t kTransFlagsOff = kTransW2Off + size_t(kC) * kHidden * 2;   // int [4], as above
 constexpr size_t kTransPackBytes = ((kTransFlagsOff + 16 + 255) / 256) * 256;
 
+// ---- triangle multiplication ---------------------------------------------------
+// Folded rows: gate a(128, pre-halved) value a(128) gate b(128, pre-halved) value b(128) of the input projections,
+// then the output gate (128, pre-halved; LayerNorm = norm_in) and the output projection (128; LayerNorm = norm_out).
+constexpr int kTriHidden = 128;
+constexpr int kTriInRows = 4 * kTriHidden;
+constexpr int kTriRows = kTriInRows + 2 * kC;
+constexpr size_t kTriWOff = 0;                                       // bf16 [768][128]
+constexpr size_t kTriScOff = kTriWOff + size_t(kTriRows) * kC * 2;   // float2 [768] {rowsum, const}
+constexpr size_t kTriFlagsOff = kTriScOff + size_t(kTriRows) * 8;    // int [4]
+constexpr size_t kTriPackBytes = ((kTriFlagsOff + 16 + 255) / 256) * 256;
+
 }  // namespace b200ta

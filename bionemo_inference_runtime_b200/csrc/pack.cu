@@ -108,6 +108,47 @@ int b200ta_pack_node_weights(const void* ln_w, const void* ln_b, const void* w_i
   return B200TA_OK;
 }
 
+size_t b200ta_trimul_pack_bytes(void) { return b200ta::kTriPackBytes; }
+
+int b200ta_pack_trimul_weights(const void* ln_in_w, const void* ln_in_b, const void* w_p_in, const void* b_p_in,
+                               const void* w_g_in, const void* b_g_in, const void* ln_out_w, const void* ln_out_b,
+                               const void* w_p_out, const void* b_p_out, const void* w_g_out, const void* b_g_out,
+                               int weight_dtype, void* packed, void* stream) {
+  using namespace b200ta;
+  B200TA_REQUIRE(ln_in_w && ln_in_b && w_p_in && w_g_in && ln_out_w && ln_out_b && w_p_out && w_g_out && packed,
+                 "pack_trimul_weights: NULL pointer");
+  B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "pack_trimul_weights: packed must be 256-byte aligned");
+  int rc = check_dtype(weight_dtype);
+  if (rc != B200TA_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* base = static_cast<char*>(packed);
+  __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>(base + kTriWOff);
+  float2* sc = reinterpret_cast<float2*>(base + kTriScOff);
+  int* flags = reinterpret_cast<int*>(base + kTriFlagsOff);
+  const size_t elem = weight_dtype == B200TA_DTYPE_F32 ? 4 : 2;
+  auto rows_of = [elem](const void* w, size_t row0) -> const void* {
+    return w == nullptr ? nullptr : static_cast<const char*>(w) + row0 * kC * elem;
+  };
+  auto vec_of = [elem](const void* v, size_t i0) -> const void* {
+    return v == nullptr ? nullptr : static_cast<const char*>(v) + i0 * elem;
+  };
+  constexpr int H = kTriHidden;
+  // gate rows are halved: sigmoid(g) = 0.5 * tanh(g / 2) + 0.5
+  for (int half = 0; half < 2; ++half) {  // a channels, then b channels
+    fold_rows_kernel<<<H, kC, 0, s>>>(rows_of(w_g_in, half * H), H, nullptr, 0, vec_of(b_g_in, half * H), ln_in_w, ln_in_b,
+                                      weight_dtype, 0, H, 0.5f, wp + size_t(half * 2 * H) * kC, sc + half * 2 * H, flags);
+    fold_rows_kernel<<<H, kC, 0, s>>>(rows_of(w_p_in, half * H), H, nullptr, 0, vec_of(b_p_in, half * H), ln_in_w, ln_in_b,
+                                      weight_dtype, 0, 0, 1.f, wp + size_t(half * 2 * H + H) * kC, sc + half * 2 * H + H,
+                                      flags);
+  }
+  fold_rows_kernel<<<kC, kC, 0, s>>>(w_g_out, kC, nullptr, 0, b_g_out, ln_in_w, ln_in_b, weight_dtype, 0, kC, 0.5f,
+                                     wp + size_t(kTriInRows) * kC, sc + kTriInRows, flags);
+  fold_rows_kernel<<<kC, kC, 0, s>>>(w_p_out, kC, nullptr, 0, b_p_out, ln_out_w, ln_out_b, weight_dtype, 0, 0, 1.f,
+                                     wp + size_t(kTriInRows + kC) * kC, sc + kTriInRows + kC, flags);
+  B200TA_CHECK_CUDA(cudaGetLastError());
+  return B200TA_OK;
+}
+
 int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const void* w1, const void* w2,
                                    int weight_dtype, void* packed, void* stream) {
   using namespace b200ta;

@@ -280,3 +280,79 @@ def transition(x: torch.Tensor, packed: torch.Tensor, mask: torch.Tensor | None 
     _lib.call("b200ta_transition", x2.data_ptr(), C, _ptr(mask), packed.data_ptr(), float(eps), out.data_ptr(), C,
               x2.shape[0], 1 if residual else 0, _stream())
     return out
+
+
+# ------------------------------------------------------------------------------------------ triangle multiplication
+
+TRI_HIDDEN = 128
+
+
+def pad16(n: int) -> int:
+    return -(-n // 16) * 16
+
+
+def pack_trimul_weights(ln_in_w, ln_in_b, w_p_in, b_p_in, w_g_in, b_g_in, ln_out_w, ln_out_b, w_p_out, b_p_out, w_g_out,
+                        b_g_out) -> torch.Tensor:
+    """Fold norm_in into p_in / g_in / g_out and norm_out into p_out; returns the opaque packed buffer."""
+    ts = [_contig(t) for t in (ln_in_w, ln_in_b, w_p_in, b_p_in, w_g_in, b_g_in, ln_out_w, ln_out_b, w_p_out, b_p_out,
+                               w_g_out, b_g_out)]
+    if (tuple(ts[2].shape) != (2 * TRI_HIDDEN, C) or tuple(ts[4].shape) != (2 * TRI_HIDDEN, C)
+            or tuple(ts[8].shape) != (C, TRI_HIDDEN) or tuple(ts[10].shape) != (C, C)):
+        raise ValueError(f"kernels are specialised for dim={C}, hidden_dim={TRI_HIDDEN}: got p_in {tuple(ts[2].shape)}, "
+                         f"g_in {tuple(ts[4].shape)}, p_out {tuple(ts[8].shape)}, g_out {tuple(ts[10].shape)}")
+    dt = _weight_dtype(*ts)
+    packed = torch.empty(_lib.load().b200ta_trimul_pack_bytes(), dtype=torch.uint8, device=ts[2].device)
+    _lib.call("b200ta_pack_trimul_weights", *[_ptr(t) for t in ts], dt, packed.data_ptr(), _stream())
+    return packed
+
+
+def _mask_strides(mask: torch.Tensor | None, B: int, I: int, J: int, swap: bool):
+    if mask is None:
+        return None, (0, 0, 0)
+    if mask.dtype != torch.float32 or not mask.is_cuda or tuple(mask.shape) != (B, I, J):
+        raise ValueError(f"mask must be a CUDA float32 tensor of shape {(B, I, J)}, got {mask.dtype} {tuple(mask.shape)}")
+    sb, si, sj = mask.stride()
+    return mask, ((sb, sj, si) if swap else (sb, si, sj))
+
+
+def trimul_project(z: torch.Tensor, mask: torch.Tensor | None, packed: torch.Tensor, eps: float = 1e-5, *,
+                   incoming: bool = False, b_scale: torch.Tensor | None = None,
+                   ab: torch.Tensor | None = None) -> torch.Tensor:
+    """Gated, masked input projection, channel-major: returns ``ab [B, 256, N, pitch]`` (a planes, then b planes;
+    the contraction index is the last axis).  ``incoming`` walks ``z`` and ``mask`` through swapped pair strides."""
+    _require_cuda_bf16("z", z)
+    B, R, S, sb, sr, ss = _pair_strides(z, incoming)
+    if R != S:
+        raise ValueError("triangle multiplication needs a square pair tensor")
+    pitch = pad16(S)
+    if ab is None:
+        ab = torch.empty((B, 2 * TRI_HIDDEN, R, pitch), dtype=torch.bfloat16, device=z.device)
+    mask, ms = _mask_strides(mask, B, z.shape[1], z.shape[2], incoming)
+    _lib.call("b200ta_trimul_project", z.data_ptr(), sb, sr, ss, _ptr(mask), *ms, _ptr(b_scale), packed.data_ptr(),
+              float(eps), ab.data_ptr(), pitch, B, R, S, _stream())
+    return ab
+
+
+def trimul_contract(ab: torch.Tensor, N: int, x: torch.Tensor | None = None) -> torch.Tensor:
+    """``x[b, d, i, j] = sum_k a[b, d, i, k] * b[b, d, j, k]`` on the planes ``trimul_project`` wrote."""
+    B, _, _, pitch = ab.shape
+    if x is None:
+        x = torch.empty((B, TRI_HIDDEN, N, pitch), dtype=torch.bfloat16, device=ab.device)
+    _lib.call("b200ta_trimul_contract", ab.data_ptr(), x.data_ptr(), B, N, pitch, _stream())
+    return x
+
+
+def trimul_output(z: torch.Tensor, x: torch.Tensor, packed: torch.Tensor, eps: float = 1e-5, *, residual: bool = False,
+                  mask: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Output normalisation, projection and gate (+ ``z``, then ``* mask`` when a mask is given)."""
+    _require_cuda_bf16("z", z)
+    B, I, J, sb, si, sj = _pair_strides(z, False)
+    if out is None:
+        out = torch.empty((B, I, J, C), dtype=torch.bfloat16, device=z.device)
+    oB, oI, oJ, osb, osi, osj = _pair_strides(out, False)
+    if (oB, oI, oJ) != (B, I, J):
+        raise ValueError(f"out has shape {tuple(out.shape)}, expected {(B, I, J, C)}")
+    mask, ms = _mask_strides(mask, B, I, J, False)
+    _lib.call("b200ta_trimul_output", z.data_ptr(), sb, si, sj, x.data_ptr(), x.shape[-1], _ptr(mask), *ms,
+              packed.data_ptr(), float(eps), 1 if residual else 0, out.data_ptr(), osb, osi, osj, B, I, _stream())
+    return out

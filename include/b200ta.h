@@ -216,6 +216,59 @@ int b200ta_node_forward_static(const void* z, int64_t zs_b, int64_t zs_r, int64_
 int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* packed, float eps,
                       void* out, int64_t os, int64_t rows, int add_residual, void* stream);
 
+/* ---- triangle multiplication ---------------------------------------------------------
+ *
+ * update = sigmoid(LN_in(z)·W_goᵀ) ⊙ ( LN_out(t)·W_poᵀ ),   t[b,i,j,d] = Σ_k a[b,i,k,d]·b[b,j,k,d]  (outgoing)
+ *                                                                       Σ_k a[b,k,i,d]·b[b,k,j,d]  (incoming)
+ * [a|b] = sigmoid(LN_in(z)·W_giᵀ) ⊙ (LN_in(z)·W_piᵀ) ⊙ mask;  dim 128, hidden 128, bf16.
+ * Three kernels with two channel-major intermediates the caller provides:
+ *   ab [B][256][N][pitch]  bf16   a planes (0..127) then b planes; contraction index contiguous
+ *   x  [B][128][N][pitch]  bf16   x[b][d][i][j]
+ * pitch % 16 == 0, pitch >= N; both 32-byte aligned.
+ *
+ * Replaces: TriangleMultiplicationNode._forward_impl (bionemo_ir/_torch/layers/triangle_nodes.py:646-727), i.e.
+ * layer_norm_transpose + dual_gemm_x_x (custom_ops/dual_gemm_x_x/ops.py:34-58) -> project,
+ * _contract_projection (triangle_nodes.py:596-612) -> contract,
+ * layer_norm_transpose + dual_gemm_x0_x1 (custom_ops/dual_gemm_x0_x1/ops.py:29-52) -> output;
+ * the same split as the reference's own fused chain trimul_kf_k1/k2/k3 (triangle_nodes.py:551-594).
+ */
+size_t b200ta_trimul_pack_bytes(void);
+
+/*
+ * Folds norm_in into p_in/g_in (rows a then b, as torch.chunk splits them) and into g_out, norm_out into p_out.
+ * All tensors share weight_dtype; biases may be NULL.  p_in/g_in: [256,128]; p_out, g_out: [128,128].
+ * Source of the parameters: triangle_nodes.py:378-417.
+ */
+int b200ta_pack_trimul_weights(const void* ln_in_w, const void* ln_in_b, const void* w_p_in, const void* b_p_in,
+                               const void* w_g_in, const void* b_g_in, const void* ln_out_w, const void* ln_out_b,
+                               const void* w_p_out, const void* b_p_out, const void* w_g_out, const void* b_g_out,
+                               int weight_dtype, void* packed, void* stream);
+
+/*
+ * ab = gated, masked input projection of z[B,R,S,128] (element strides zs_*), written channel-major with S
+ * contiguous.  The outgoing node passes z as it is (R = i, S = k); the incoming node passes the two pair strides
+ * swapped (R = i read along the second pair axis, S = k along the first), and the mask likewise.
+ *   mask     fp32, element (b,r,s) at b*ms_b + r*ms_r + s*ms_s, or NULL (all ones).
+ *   b_scale  fp32 [B] multiplying the b channels (mean normalisation: 1 / (n_valid + 1e-3)), or NULL.
+ */
+int b200ta_trimul_project(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, const float* mask, int64_t ms_b,
+                          int64_t ms_r, int64_t ms_s, const float* b_scale, const void* packed, float eps, void* ab,
+                          int64_t pitch, int B, int R, int S, void* stream);
+
+/* x[b][d][i][j] = Σ_k ab[b][d][i][k] * ab[b][128+d][j][k]  (fp32 accumulation, bf16 result). */
+int b200ta_trimul_contract(const void* ab, void* x, int B, int N, int64_t pitch, void* stream);
+
+/*
+ * out[b,i,j,:] = sigmoid(LN_in(z)·W_goᵀ + b_go) ⊙ (LN_out(x[b,:,i,j])·W_poᵀ + b_po)  [+ z]  [then * mask]
+ * z and out in the caller's orientation [B,N,N,128] via element strides (multiples of 16, 32-byte aligned bases);
+ * out may alias z.  mask (fp32, strides ms_*) multiplies the result as the reference's fused residual kernel does
+ * (tests/_torch/test_triangle_nodes.py:272-311); NULL leaves it unmasked like the unfused path.
+ */
+int b200ta_trimul_output(const void* z, int64_t zs_b, int64_t zs_i, int64_t zs_j, const void* x, int64_t pitch,
+                         const float* mask, int64_t ms_b, int64_t ms_i, int64_t ms_j, const void* packed, float eps,
+                         int add_residual, void* out, int64_t os_b, int64_t os_i, int64_t os_j, int B, int N,
+                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif
