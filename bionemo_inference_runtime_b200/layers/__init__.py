@@ -8,6 +8,9 @@ from .auto_chunk import (CHUNK_REGISTRY, PAIR_TRANSITION, TRIANGLE_ATTENTION, Ch
 from .buffers import PreallocatedBuffers, ensure_buffer
 from .linear import Linear, WeightMode, WeightsLoadingConfig
 from .transition import Transition
+from .triangle_multiplication import (TriangleMultiplicationMetadata, TriangleMultiplicationNode,
+                                      TriangleMultiplicationNodeType, precompute_trimul_metadata,
+                                      set_trimul_token_padding)
 from .triangle_nodes import (TriangleAttention, TriangleAttentionEndingNode, TriangleAttentionNode,
                              TriangleAttentionNodeType, TriangleAttentionStartingNode, split_pair_bias_proj)
 
@@ -18,4 +21,6 @@ __all__ = [
     "chunk_apply", "default_autochunk_min", "iter_chunks", "PreallocatedBuffers", "ensure_buffer", "Linear",
     "WeightMode", "WeightsLoadingConfig", "Transition", "TriangleAttention", "TriangleAttentionEndingNode",
     "TriangleAttentionNode", "TriangleAttentionNodeType", "TriangleAttentionStartingNode", "split_pair_bias_proj",
+    "TriangleMultiplicationMetadata", "TriangleMultiplicationNode", "TriangleMultiplicationNodeType",
+    "precompute_trimul_metadata", "set_trimul_token_padding",
 ]

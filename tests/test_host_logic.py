@@ -119,3 +119,29 @@ def test_ensure_buffer_reuses_and_reallocates():
     assert b200.ensure_buffer(bufs, "k", (2, 3), torch.float32, torch.device("cpu")) is a
     assert b200.ensure_buffer(bufs, "k", (2, 4), torch.float32, torch.device("cpu")) is not a
     assert b200.ensure_buffer(None, "k", (2, 3), torch.float32, torch.device("cpu")) is None
+
+
+def test_triangle_multiplication_state_dict_keys_dtypes_and_errors():
+    """Keys and shapes of the reference module (bionemo_ir/_torch/layers/triangle_nodes.py:378-417)."""
+    node = b200.TriangleMultiplicationNode(dtype=torch.bfloat16, high_precision=False)
+    shapes = {k: tuple(v.shape) for k, v in node.state_dict().items()}
+    assert shapes == {"norm_in.weight": (128,), "norm_in.bias": (128,), "p_in.weight": (256, 128),
+                      "g_in.weight": (256, 128), "norm_out.weight": (128,), "norm_out.bias": (128,),
+                      "p_out.weight": (128, 128), "g_out.weight": (128, 128)}
+    assert all(not p.requires_grad for n, p in node.named_parameters() if "norm" not in n)
+    hp = b200.TriangleMultiplicationNode(dtype=torch.bfloat16, bias_flags={"p_in": True, "g_in": True, "p_out": True,
+                                                                        "g_out": True}, norm_bias=False)
+    sd = hp.state_dict()
+    assert "norm_in.bias" not in sd and sd["p_in.bias"].shape == (256,) and sd["g_out.bias"].dtype == torch.float32
+    assert sd["norm_out.weight"].dtype == torch.float32 and sd["norm_in.weight"].dtype == torch.bfloat16
+    assert int(b200.TriangleMultiplicationNodeType.OUTGOING) == 0 and int(b200.TriangleMultiplicationNodeType.INCOMING) == 1
+    with pytest.raises(ValueError):
+        b200.TriangleMultiplicationNode(dim=64)
+    with pytest.raises(ValueError):
+        node(torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16), None)  # no CPU path
+    meta = b200.precompute_trimul_metadata(torch.zeros(1, 9, 9, 128), torch.ones(1, 9, dtype=torch.int32), None)
+    assert meta.token_pad_multiple == -1 and meta.outgoing_actual_seqlen is not None
+    assert b200.precompute_trimul_metadata(torch.zeros(1, 9, 9, 128), torch.ones(1, 9), None,
+                                           enabled=False).outgoing_actual_seqlen is None
+    b200.set_trimul_token_padding(torch.nn.Sequential(node), True)
+    assert node.pad_tokens is True
