@@ -41,11 +41,14 @@ WORKLOADS = {
                  desc="start+end TriangleAttention + transition, z[64,256,256,128] bf16, valid ~U{160..256} (BASELINE config 3)"),
     "n768": dict(B=1, N=768, valid="768", transition=True,
                  desc="start+end TriangleAttention + transition, z[1,768,768,128] bf16, all valid (pair track of BASELINE config 4)"),
+    "block768": dict(B=1, N=768, valid="768", transition=True, trimul=True,
+                     desc="pair track of one Pairformer block: triangle multiplication outgoing + incoming, "
+                          "start+end TriangleAttention, transition, z[1,768,768,128] bf16, all valid (BASELINE config 4)"),
     "cfg5": dict(B=1, N=4096, valid="3900", transition=True, sharded=True, blocks=4,
                  desc="4 x (start node, all-to-all, end node, transition), z[1,4096,4096,128] bf16 row-sharded over the "
                       "GPUs, 3900 valid tokens (BASELINE config 5)"),
 }
-DEFAULT_STEPS = {"cfg2": 100, "cfg3": 20, "n768": 50, "cfg5": 3}
+DEFAULT_STEPS = {"cfg2": 100, "cfg3": 20, "n768": 50, "block768": 50, "cfg5": 3}
 
 
 def valid_lengths(spec: str, B: int, N: int, gen: torch.Generator) -> list[int]:
@@ -66,6 +69,12 @@ def attention_core_flops(L: int) -> float:
 
 def transition_flops(L: int) -> float:
     return float(L) * L * 393216.0
+
+
+def trimul_flops(L: int, N: int) -> float:
+    """One triangle-multiplication node: projections (128 -> 2x256, 2x 128 -> 128) on the L² valid positions plus the
+    contraction, 2·L flops per valid position and channel (128 channels)."""
+    return float(L) * L * (131072.0 + 65536.0 + 256.0 * L)
 
 
 def measured_peaks() -> tuple[float, float, str]:
@@ -178,6 +187,21 @@ def build_modules(w_start, w_end, w_tr, device):
     return start, end, tr.to(device)
 
 
+def build_trimul(seed: int, device):
+    import bionemo_inference_runtime_b200 as b200
+    from oracle import triangle_oracle as orc  # weight recipe only
+
+    nodes = []
+    for k, kind in enumerate((b200.TriangleMultiplicationNodeType.OUTGOING, b200.TriangleMultiplicationNodeType.INCOMING)):
+        w = orc.make_trimul_weights(seed + 10 + k)
+        n = b200.TriangleMultiplicationNode(multiplication_type=kind, dtype=torch.bfloat16, high_precision=False)
+        n.load_state_dict({"norm_in.weight": w.ln_in_w, "norm_in.bias": w.ln_in_b, "p_in.weight": w.w_p_in,
+                           "g_in.weight": w.w_g_in, "norm_out.weight": w.ln_out_w, "norm_out.bias": w.ln_out_b,
+                           "p_out.weight": w.w_p_out, "g_out.weight": w.w_g_out}, strict=True)
+        nodes.append(n.to(device))
+    return nodes
+
+
 def run_ours(args) -> dict:
     import torch.distributed as dist
 
@@ -197,17 +221,23 @@ def run_ours(args) -> dict:
     pre = b200.precompute_pair_masks("Heuristic", mask_host.to(device))
     z_dev = z_host.to(device)
     bufs: dict = {}
+    trimul = build_trimul(1000 + rank, device) if cfg.get("trimul") else []
+    mask_dev = mask_host.to(device)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
 
-    def step(z):
-        z1 = start(z, mask_bias=pre.mask_bias, buffers=bufs, residual=True)
-        z2 = end(z1, mask_bias=pre.mask_bias_transposed, buffers=bufs, residual=True, inplace_residual=True)
+    def step(z, b=None):
+        b = bufs if b is None else b
+        for tm in trimul:  # Pairformer order: triangle multiplication out, in, then the attention nodes
+            z = tm(z, mask_dev, residual=True, buffers=b)
+        z1 = start(z, mask_bias=pre.mask_bias, buffers=b, residual=True)
+        z2 = end(z1, mask_bias=pre.mask_bias_transposed, buffers=b, residual=True, inplace_residual=True)
         if cfg["transition"]:
             z2 = trans(z2, residual=True, inplace=True)
         return z2
 
-    launches_per_step = 6 + (1 if cfg["transition"] else 0)
-    flops_step = sum(2 * node_flops(L) + (transition_flops(L) if cfg["transition"] else 0.0) for L in lens)
+    launches_per_step = 6 + (1 if cfg["transition"] else 0) + 3 * len(trimul)
+    flops_step = sum(2 * node_flops(L) + (transition_flops(L) if cfg["transition"] else 0.0)
+                     + len(trimul) * trimul_flops(L, cfg["N"]) for L in lens)
 
     def barrier():
         if world > 1:
@@ -264,11 +294,7 @@ def run_ours(args) -> dict:
     slot_bufs: list[dict] = [{}, {}]
 
     def slot_step(zd, slot):
-        z1 = start(zd, mask_bias=pre.mask_bias, buffers=slot_bufs[slot], residual=True)
-        z2 = end(z1, mask_bias=pre.mask_bias_transposed, buffers=slot_bufs[slot], residual=True, inplace_residual=True)
-        if cfg["transition"]:
-            z2 = trans(z2, residual=True, inplace=True)
-        return z2
+        return step(zd, slot_bufs[slot])
 
     pipe = b200.HostPipeline(slot_step, z_pin, device, depth=2)
     pipe.run([z_pin] * 4, [outs_pin[i & 1] for i in range(4)])  # warm-up
@@ -336,7 +362,7 @@ def run_ours(args) -> dict:
                      "peak_source": f"{peak_kind} bf16 burst", "ms_per_launch": attn_ms, "traffic": TRAFFIC.get(args.workload)},
         "clocks": clocks.summary(),
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not cfg.get("trimul"):  # the CPU sample covers rows of the attention nodes and the transition only
         result["cpu_baseline"] = cpu_baseline(cfg, args.workload)
     if world > 1:
         dist.barrier()
