@@ -145,3 +145,48 @@ def test_triangle_multiplication_state_dict_keys_dtypes_and_errors():
                                            enabled=False).outgoing_actual_seqlen is None
     b200.set_trimul_token_padding(torch.nn.Sequential(node), True)
     assert node.pad_tokens is True
+
+
+def test_boltz_checkpoint_converters_feed_strict_loads():
+    """Key mappings of bionemo_ir/models/convert_utils.py:29-98 into this package's layers."""
+    from bionemo_inference_runtime_b200 import convert_utils as cu
+
+    g = torch.Generator().manual_seed(0)
+    r = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    ckpt = {}
+    p = "layers.0.tri_att_start"
+    for k, shape in {"layer_norm.weight": (128,), "layer_norm.bias": (128,), "linear.weight": (4, 128),
+                     "mha.linear_q.weight": (128, 128), "mha.linear_k.weight": (128, 128),
+                     "mha.linear_v.weight": (128, 128), "mha.linear_g.weight": (128, 128),
+                     "mha.linear_o.weight": (128, 128)}.items():
+        ckpt[f"{p}.{k}"] = r(*shape)
+    sd = cu.get_tri_attn_node_weights(ckpt, p, "blk.tri_attn_start", dtype="bfloat16")
+    node = b200.TriangleAttentionStartingNode(128, 32, 4, dtype=torch.bfloat16)
+    node.load_state_dict({k.removeprefix("blk.tri_attn_start."): v for k, v in sd.items()}, strict=True)
+    w = node.mha.in_proj.weight.float()
+    assert torch.equal(w[128:256], ckpt[f"{p}.mha.linear_k.weight"].bfloat16().float())
+    assert torch.equal(w[384:], ckpt[f"{p}.mha.linear_g.weight"].bfloat16().float())
+    assert torch.equal(node.pair_bias_proj.weight.float(), ckpt[f"{p}.linear.weight"].bfloat16().float())
+
+    p = "layers.0.tri_mul_out"
+    for k, shape in {"norm_in.weight": (128,), "norm_in.bias": (128,), "p_in.weight": (256, 128), "g_in.weight": (256, 128),
+                     "norm_out.weight": (128,), "norm_out.bias": (128,), "p_out.weight": (128, 128),
+                     "g_out.weight": (128, 128)}.items():
+        ckpt[f"{p}.{k}"] = r(*shape)
+    sd = cu.get_tri_mul_node_weights(ckpt, p, "m", dtype="bfloat16")
+    assert sd["m.p_in.weight"].dtype == torch.bfloat16 and sd["m.p_out.weight"].dtype == torch.float32
+    tm = b200.TriangleMultiplicationNode(dtype=torch.bfloat16, high_precision=True)
+    tm.load_state_dict({k.removeprefix("m."): v for k, v in sd.items()}, strict=True)
+    assert torch.equal(tm.g_out.weight, ckpt[f"{p}.g_out.weight"])
+
+    p = "layers.0.transition_z"
+    for k, shape in {"norm.weight": (128,), "norm.bias": (128,), "fc1.weight": (512, 128), "fc2.weight": (512, 128),
+                     "fc3.weight": (128, 512)}.items():
+        ckpt[f"{p}.{k}"] = r(*shape)
+    sd = cu.get_transition_weights(ckpt, p, "t", dtype="bfloat16")
+    tr = b200.Transition(128, 512, dtype=torch.bfloat16)
+    tr.load_state_dict({k.removeprefix("t."): v for k, v in sd.items()}, strict=True)
+    assert torch.equal(tr.fused_fc2_fc1.weight[:512].float(), ckpt[f"{p}.fc2.weight"].bfloat16().float())  # value rows first
+    assert torch.equal(tr.fused_fc2_fc1.weight[512:].float(), ckpt[f"{p}.fc1.weight"].bfloat16().float())  # then gate rows
+    with pytest.raises(ValueError):
+        cu.get_transition_weights(ckpt, p, "t", dtype="int7")
