@@ -260,48 +260,60 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
       const int i = bi % p.N, b = bi / p.N;
       const int stage = it & 1, slot = it & 1;
       const int j = jt * kTileM + m;
+      // The residual values do not depend on the accumulators: fetch this thread's 2 x 32 channels (they were just
+      // loaded as part of the z tile, so they come from L2) before waiting for the MMAs.
+      uint32_t res[2][16];
+#pragma unroll
+      for (int gi = 0; gi < 2; ++gi) {
+        if (p.add_residual && j < p.N) {
+          const uint4* rp = reinterpret_cast<const uint4*>(p.z + b * p.zs_b + i * p.zs_i + (long long)j * p.zs_j +
+                                                           (e + 2 * gi) * 32);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 x = __ldg(rp + c);
+            res[gi][c * 4 + 0] = x.x, res[gi][c * 4 + 1] = x.y, res[gi][c * 4 + 2] = x.z, res[gi][c * 4 + 3] = x.w;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) res[gi][c] = 0u;
+        }
+      }
       ok = mbar_wait(bars + (ACC_FULL + slot) * 8, (it >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
       const float4 stv = reinterpret_cast<const float4*>(gen + kSmStats + stage * 2048)[m];
       const float rstd = stv.x, nmr = stv.y, mval = stv.z;
+      // four chunks of 16 output channels: [32 g + 16 h, +16) for this warpgroup's groups g = e, e + 2; the TMEM
+      // loads of the next chunk are in flight while this one is computed
+      uint32_t ag[2][16], ap[2][16];
+      const uint32_t acc = lane_taddr + slot * 256;
+      tmem_ld16(acc + e * 32, ag[0]);
+      tmem_ld16(acc + 128 + e * 32, ap[0]);
 #pragma unroll
-      for (int gi = 0; gi < 2; ++gi) {
-        const int g = e + 2 * gi;  // 32 output channels [32 g, 32 g + 32)
-        uint32_t ag[32], ap[32];
-        tmem_ld32(lane_taddr + slot * 256 + g * 32, ag);
-        tmem_ld32(lane_taddr + slot * 256 + 128 + g * 32, ap);
-        uint32_t res[16];
-        if (p.add_residual && j < p.N) {
-          const uint4* rp = reinterpret_cast<const uint4*>(p.z + b * p.zs_b + i * p.zs_i + (long long)j * p.zs_j + g * 32);
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const uint4 x = __ldg(rp + c);
-            res[c * 4 + 0] = x.x, res[c * 4 + 1] = x.y, res[c * 4 + 2] = x.z, res[c * 4 + 3] = x.w;
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) res[c] = 0u;
-        }
+      for (int ck = 0; ck < 4; ++ck) {
+        const int g = e + 2 * (ck >> 1), h = ck & 1;
+        const int ch0 = g * 32 + h * 16;
         tmem_ld_wait();
-        uint32_t packed[16];
+        if (ck + 1 < 4) {
+          const int gn = e + 2 * ((ck + 1) >> 1), hn = (ck + 1) & 1;
+          tmem_ld16(acc + gn * 32 + hn * 16, ag[(ck + 1) & 1]);
+          tmem_ld16(acc + 128 + gn * 32 + hn * 16, ap[(ck + 1) & 1]);
+        }
+        const uint32_t (&xg)[16] = ag[ck & 1];
+        const uint32_t (&xp)[16] = ap[ck & 1];
+        uint32_t packed[8];
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float4 k0 = c4[g * 32 + 2 * c], k1 = c4[g * 32 + 2 * c + 1];  // {c_gate, rowsum_p, c_p}
+        for (int c = 0; c < 8; ++c) {
+          const float4 k0 = c4[ch0 + 2 * c], k1 = c4[ch0 + 2 * c + 1];  // {c_gate, rowsum_p, c_p}
           // gate rows are pre-halved: sigmoid(x) = 0.5 * tanh(x / 2) + 0.5
-          const float s0 = fmaf(0.5f, tanh_approx(__uint_as_float(ag[2 * c]) + k0.x), 0.5f);
-          const float s1 = fmaf(0.5f, tanh_approx(__uint_as_float(ag[2 * c + 1]) + k1.x), 0.5f);
-          const float v0 = fmaf(rstd, __uint_as_float(ap[2 * c]), fmaf(nmr, k0.y, k0.z));
-          const float v1 = fmaf(rstd, __uint_as_float(ap[2 * c + 1]), fmaf(nmr, k1.y, k1.z));
-          const float o0 = (fmaf(s0, v0, bf16_lo(res[c]))) * mval;
-          const float o1 = (fmaf(s1, v1, bf16_hi(res[c]))) * mval;
-          packed[c] = pack_bf16x2(o0, o1);
+          const float s0 = fmaf(0.5f, tanh_approx(__uint_as_float(xg[2 * c]) + k0.x), 0.5f);
+          const float s1 = fmaf(0.5f, tanh_approx(__uint_as_float(xg[2 * c + 1]) + k1.x), 0.5f);
+          const float v0 = fmaf(rstd, __uint_as_float(xp[2 * c]), fmaf(nmr, k0.y, k0.z));
+          const float v1 = fmaf(rstd, __uint_as_float(xp[2 * c + 1]), fmaf(nmr, k1.y, k1.z));
+          const uint32_t r = res[ck >> 1][h * 8 + c];
+          packed[c] = pack_bf16x2(fmaf(s0, v0, bf16_lo(r)) * mval, fmaf(s1, v1, bf16_hi(r)) * mval);
         }
-        if (j < p.N) {
-          __nv_bfloat16* dst = p.out + b * p.os_b + i * p.os_i + (long long)j * p.os_j + g * 32;
-          stg256(dst, packed);
-          stg256(dst + 16, packed + 8);
-        }
+        if (j < p.N) stg256(p.out + b * p.os_b + i * p.os_i + (long long)j * p.os_j + ch0, packed);
       }
       tc_fence_before();
       __syncwarp();

@@ -29,7 +29,7 @@ constexpr int kWHalf = kTriInRows * 128;    // 64 KiB
 constexpr int kSmZ = kSmW + 2 * kWHalf;     // 2 stages x 32 KiB
 constexpr int kSmMask = kSmZ + 2 * 32768;   // 2 stages x 128 floats
 constexpr int kSmBars = kSmMask + 2 * 512;
-enum Bar { W_FULL = 0, Z_FULL = 1, Z_READY = 3, Z_EMPTY = 5, ACC_FULL = 7, ACC_EMPTY = 9, NUM_BARS = 11 };
+enum Bar { W_FULL = 0, Z_FULL = 1, Z_READY = 3, Z_EMPTY = 5, ACC_FULL = 7, ACC_EMPTY = 11, NUM_BARS = 15 };
 constexpr int kSmTotal = kSmBars + 256;
 constexpr int kSmDynamic = kSmTotal + 1024;
 
@@ -70,7 +70,9 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       mbar_init(bars + (Z_FULL + i) * 8, 1);
       mbar_init(bars + (Z_READY + i) * 8, 4);   // the four normaliser warps
       mbar_init(bars + (Z_EMPTY + i) * 8, 9);   // the MMA commit + the eight epilogue warps (they read the mask)
-      mbar_init(bars + (ACC_FULL + i) * 8, 1);  // per warpgroup
+    }
+    for (int i = 0; i < 4; ++i) {  // per (warpgroup, half of the tile's positions)
+      mbar_init(bars + (ACC_FULL + i) * 8, 1);
       mbar_init(bars + (ACC_EMPTY + i) * 8, 4);
     }
     fence_mbar_init();
@@ -112,27 +114,32 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
   } else if (warp == 13) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(128, kTileM);
+      // Each accumulator covers 64 of the tile's 128 positions, so that the MMAs of one half overlap the epilogue
+      // of the other: TMEM columns (warpgroup, half, gate | value) x 64.
+      constexpr uint32_t idesc = make_idesc_bf16(128, kTileM / 2);
       bool ok = mbar_wait(bars + W_FULL * 8, 0, abort_flag);
       for (int i = 0; ok && i < my_tiles; ++i) {
         const int stage = i & 1;
         ok = mbar_wait(bars + (Z_READY + stage) * 8, (i >> 1) & 1, abort_flag);
         if (!ok) break;
-        const uint64_t dz = make_smem_desc(base + kSmZ + stage * 32768, 16, 1024, kLayoutSw128);
-        for (int wg = 0; ok && wg < 2; ++wg) {
-          ok = mbar_wait(bars + (ACC_EMPTY + wg) * 8, (i & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
+        for (int half = 0; ok && half < 2; ++half) {
+          // rows 64 half .. of the [128 positions][64 channels] blocks: 8 KiB further
+          const uint64_t dz = make_smem_desc(base + kSmZ + stage * 32768 + half * 8192, 16, 1024, kLayoutSw128);
+          for (int wg = 0; ok && wg < 2; ++wg) {
+            ok = mbar_wait(bars + (ACC_EMPTY + wg * 2 + half) * 8, (i & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
-          for (int acc = 0; acc < 2; ++acc) {  // gate rows, then value rows of this warpgroup's channels
-            const uint32_t d = tmem_base + (wg * 2 + acc) * 128;
-            const uint64_t dw = make_smem_desc(base + kSmW + (wg * 2 + acc) * 128 * 128, 16, 1024, kLayoutSw128);
+            for (int acc = 0; acc < 2; ++acc) {  // gate rows, then value rows of this warpgroup's channels
+              const uint32_t d = tmem_base + (wg * 2 + half) * 128 + acc * 64;
+              const uint64_t dw = make_smem_desc(base + kSmW + (wg * 2 + acc) * 128 * 128, 16, 1024, kLayoutSw128);
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-              umma_ss(d, dw + ((k >> 2) * (kWHalf >> 4) + (k & 3) * 2), dz + ((k >> 2) * (16384 >> 4) + (k & 3) * 2), idesc,
-                      k > 0 ? 1u : 0u);
+              for (int k = 0; k < 8; ++k)
+                umma_ss(d, dw + ((k >> 2) * (kWHalf >> 4) + (k & 3) * 2), dz + ((k >> 2) * (16384 >> 4) + (k & 3) * 2),
+                        idesc, k > 0 ? 1u : 0u);
+            }
+            umma_commit(bars + (ACC_FULL + wg * 2 + half) * 8);
           }
-          umma_commit(bars + (ACC_FULL + wg) * 8);
         }
         if (!ok) break;
         umma_commit(bars + (Z_EMPTY + stage) * 8);
@@ -207,42 +214,54 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       const int r = br % p.R, b = br / p.R;
       const int stage = i & 1;
       const float bscale = (wg == 1 && p.b_scale) ? __ldg(p.b_scale + b) : 1.f;
-      ok = mbar_wait(bars + (ACC_FULL + wg) * 8, i & 1, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
       const float4* mk = reinterpret_cast<const float4*>(gen + kSmMask + stage * 512);
       __nv_bfloat16* dst = p.ab + ((long long)(b * 2 + wg) * kTriHidden + ch) * p.R * p.pitch + (long long)r * p.pitch +
                            st * kTileM;
-#pragma unroll 1
-      for (int part = 0; part < 8; ++part) {  // 16 positions at a time
-        uint32_t g[16], v[16];
-        tmem_ld16(lane_taddr + part * 16, g);
-        tmem_ld16(lane_taddr + 128 + part * 16, v);
-        float mv[16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float4 t = mk[part * 4 + j];
-          mv[4 * j] = t.x * bscale, mv[4 * j + 1] = t.y * bscale, mv[4 * j + 2] = t.z * bscale, mv[4 * j + 3] = t.w * bscale;
-        }
-        tmem_ld_wait();
-        uint32_t packed[8];
+      for (int half = 0; half < 2; ++half) {
+        ok = mbar_wait(bars + (ACC_FULL + wg * 2 + half) * 8, i & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t acc = lane_taddr + half * 128;  // gate columns, the value columns follow 64 further
+        // 16 positions at a time; the TMEM loads of the next chunk are in flight while this one is computed
+        uint32_t g[2][16], v[2][16];
+        tmem_ld16(acc, g[0]);
+        tmem_ld16(acc + 64, v[0]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          // gate rows are pre-halved: sigmoid(x) = 0.5 * tanh(x / 2) + 0.5
-          const float s0 = fmaf(0.5f, tanh_approx(__uint_as_float(g[2 * j]) + cg), 0.5f);
-          const float s1 = fmaf(0.5f, tanh_approx(__uint_as_float(g[2 * j + 1]) + cg), 0.5f);
-          const float o0 = s0 * (__uint_as_float(v[2 * j]) + cp) * mv[2 * j];
-          const float o1 = s1 * (__uint_as_float(v[2 * j + 1]) + cp) * mv[2 * j + 1];
-          packed[j] = pack_bf16x2(o0, o1);
+        for (int part = 0; part < 4; ++part) {
+          const int pos0 = half * 64 + part * 16;
+          float mv[16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 t = mk[(pos0 >> 2) + j];
+            mv[4 * j] = t.x * bscale, mv[4 * j + 1] = t.y * bscale, mv[4 * j + 2] = t.z * bscale, mv[4 * j + 3] = t.w * bscale;
+          }
+          tmem_ld_wait();
+          if (part + 1 < 4) {
+            tmem_ld16(acc + (part + 1) * 16, g[(part + 1) & 1]);
+            tmem_ld16(acc + 64 + (part + 1) * 16, v[(part + 1) & 1]);
+          }
+          const uint32_t (&gg)[16] = g[part & 1];
+          const uint32_t (&vv)[16] = v[part & 1];
+          uint32_t packed[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            // gate rows are pre-halved: sigmoid(x) = 0.5 * tanh(x / 2) + 0.5
+            const float s0 = fmaf(0.5f, tanh_approx(__uint_as_float(gg[2 * j]) + cg), 0.5f);
+            const float s1 = fmaf(0.5f, tanh_approx(__uint_as_float(gg[2 * j + 1]) + cg), 0.5f);
+            const float o0 = s0 * (__uint_as_float(vv[2 * j]) + cp) * mv[2 * j];
+            const float o1 = s1 * (__uint_as_float(vv[2 * j + 1]) + cp) * mv[2 * j + 1];
+            packed[j] = pack_bf16x2(o0, o1);
+          }
+          if (st * kTileM + pos0 + 16 <= p.pitch) stg256(dst + pos0, packed);
         }
-        if (st * kTileM + part * 16 + 16 <= p.pitch) stg256(dst + part * 16, packed);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + (ACC_EMPTY + wg * 2 + half) * 8);
       }
-      tc_fence_before();
+      if (!ok) break;
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bars + (ACC_EMPTY + wg) * 8);
-        mbar_arrive(bars + (Z_EMPTY + stage) * 8);  // done with this stage's mask values
-      }
+      if (lane == 0) mbar_arrive(bars + (Z_EMPTY + stage) * 8);  // done with this stage's mask values
     }
   }
 
