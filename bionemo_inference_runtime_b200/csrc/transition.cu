@@ -41,7 +41,8 @@ constexpr int kSmW1 = kSmX + 2 * 32768;        // 2 x 32 KiB: [k-half][64 value 
 constexpr int kSmW2 = kSmW1 + 2 * 32768;       // 2 x 16 KiB: [128 out rows][64 hidden]
 constexpr int kSmH = kSmW2 + 2 * 16384;        // 2 x 16 KiB: [128 rows][64 hidden]
 constexpr int kSmOut = kSmH + 2 * 16384;       // 8 warps x 2 KiB staging slabs
-constexpr int kSmBars = kSmOut + 8 * 2048;
+constexpr int kSmSc = kSmOut + 8 * 2048;       // per pair of hidden units {rowsum0, rowsum1, const0, const1}: 256 value pairs, 256 gate pairs
+constexpr int kSmBars = kSmSc + 2 * 4096;
 constexpr int kSmTotal = kSmBars + 256;
 constexpr int kSmDynamic = kSmTotal + 1024;
 
@@ -84,6 +85,11 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       mbar_init(bars + (ACC2_FREE + i) * 8, 8);
     }
     fence_mbar_init();
+  }
+  // stage the per-unit constants of the folded W1 rows, two units per float4
+  for (int q = threadIdx.x; q < kHidden; q += kThreads) {  // 256 value pairs, then 256 gate pairs
+    const float2 a = p.sc[2 * q], b = p.sc[2 * q + 1];
+    reinterpret_cast<float4*>(gen + kSmSc)[q] = make_float4(a.x, b.x, a.y, b.y);
   }
   if (warp == 9) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
   tc_fence_before();
@@ -232,31 +238,43 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
              mbar_wait(bars + (H_FREE + e) * 8, (n & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const float2* scv = p.sc + j * kChunk;            // value rows of this chunk
-        const float2* scg = p.sc + kHidden + j * kChunk;  // gate rows
+        const float4* scv = reinterpret_cast<const float4*>(gen + kSmSc) + j * (kChunk / 2);               // value pairs
+        const float4* scg = reinterpret_cast<const float4*>(gen + kSmSc) + kHidden / 2 + j * (kChunk / 2);  // gate pairs
+        const uint64_t rstd2 = pack_f32x2(rstd, rstd), nmr2 = pack_f32x2(nmr, nmr);
+        // 16 hidden units at a time; the TMEM loads of the next step are in flight while this one is computed
+        uint32_t av[2][16], ag[2][16];
+        const uint32_t acc1 = lane_taddr + kTmemAcc1 + e * 128;
+        tmem_ld16(acc1, av[0]);
+        tmem_ld16(acc1 + 64, ag[0]);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t av[32], ag[32];
-          tmem_ld32(lane_taddr + kTmemAcc1 + e * 128 + half * 32, av);
-          tmem_ld32(lane_taddr + kTmemAcc1 + e * 128 + 64 + half * 32, ag);
+        for (int qt = 0; qt < 4; ++qt) {
           tmem_ld_wait();
-          uint32_t pk[16];
+          if (qt + 1 < 4) {
+            tmem_ld16(acc1 + (qt + 1) * 16, av[(qt + 1) & 1]);
+            tmem_ld16(acc1 + 64 + (qt + 1) * 16, ag[(qt + 1) & 1]);
+          }
+          const uint32_t (&xv)[16] = av[qt & 1];
+          const uint32_t (&xg)[16] = ag[qt & 1];
+          uint32_t pk[8];
 #pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            float hid[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int col = half * 32 + 2 * t + u;
-              const float2 sv = __ldg(scv + col), sg = __ldg(scg + col);
-              const float val = fmaf(rstd, __uint_as_float(av[2 * t + u]), fmaf(nmr, sv.x, sv.y));
-              const float h = fmaf(rstd, __uint_as_float(ag[2 * t + u]), fmaf(nmr, sg.x, sg.y));  // gate / 2
-              hid[u] = fmaf(h, tanh_approx(h), h) * val;  // silu(gate) * value
-            }
-            pk[t] = pack_bf16x2(hid[0], hid[1]);
+          for (int t = 0; t < 8; ++t) {
+            // two hidden units at a time, packed fp32x2 math
+            const float4 cv = scv[qt * 8 + t], cg = scg[qt * 8 + t];
+            const uint64_t val2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xv[2 * t]), __uint_as_float(xv[2 * t + 1])),
+                                            fma_f32x2(nmr2, pack_f32x2(cv.x, cv.y), pack_f32x2(cv.z, cv.w)));
+            const uint64_t h2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xg[2 * t]), __uint_as_float(xg[2 * t + 1])),
+                                          fma_f32x2(nmr2, pack_f32x2(cg.x, cg.y), pack_f32x2(cg.z, cg.w)));  // gate / 2
+            float h0, h1;
+            unpack_f32x2(h2, h0, h1);
+            // silu(gate) * value = (h * tanh(h) + h) * value
+            const uint64_t hid2 = mul_f32x2(fma_f32x2(h2, pack_f32x2(tanh_approx(h0), tanh_approx(h1)), h2), val2);
+            float o0, o1;
+            unpack_f32x2(hid2, o0, o1);
+            pk[t] = pack_bf16x2(o0, o1);
           }
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            sts128(base + kSmH + e * 16384 + sw128_offset(m, half * 4 + c),
+          for (int c = 0; c < 2; ++c)
+            sts128(base + kSmH + e * 16384 + sw128_offset(m, qt * 2 + c),
                    make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]));
         }
         tc_fence_before();
