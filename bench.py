@@ -44,11 +44,15 @@ WORKLOADS = {
     "block768": dict(B=1, N=768, valid="768", transition=True, trimul=True,
                      desc="pair track of one Pairformer block: triangle multiplication outgoing + incoming, "
                           "start+end TriangleAttention, transition, z[1,768,768,128] bf16, all valid (BASELINE config 4)"),
+    "cfg4pair": dict(B=1, N=768, valid="768", transition=True, trimul=True, blocks=48,
+                     desc="pair track of a 48-block Pairformer trunk (PairformerNoSeqModule: per block triangle "
+                          "multiplication out + in, start+end TriangleAttention, transition), z[1,768,768,128] bf16, "
+                          "all valid (pair track of BASELINE config 4), replayed from one CUDA graph"),
     "cfg5": dict(B=1, N=4096, valid="3900", transition=True, sharded=True, blocks=4,
                  desc="4 x (start node, all-to-all, end node, transition), z[1,4096,4096,128] bf16 row-sharded over the "
                       "GPUs, 3900 valid tokens (BASELINE config 5)"),
 }
-DEFAULT_STEPS = {"cfg2": 100, "cfg3": 20, "n768": 50, "block768": 50, "cfg5": 3}
+DEFAULT_STEPS = {"cfg2": 100, "cfg3": 20, "n768": 50, "block768": 50, "cfg4pair": 5, "cfg5": 3}
 
 
 def valid_lengths(spec: str, B: int, N: int, gen: torch.Generator) -> list[int]:
@@ -225,7 +229,21 @@ def run_ours(args) -> dict:
     mask_dev = mask_host.to(device)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
 
+    stack = None
+    if cfg.get("blocks") and not cfg.get("sharded"):
+        # a whole trunk: the package's stack module with random weights per block, one CUDA graph for all blocks
+        stack = b200.PairformerNoSeqModule(num_blocks=cfg["blocks"], dtype=torch.bfloat16, triangle_attn_backend="Heuristic",
+                                           trimul_high_precision=False, use_cuda_graph=True).to(device)
+        gen = torch.Generator(device=device).manual_seed(2000 + rank)
+        for name, prm in stack.named_parameters():
+            if prm.dim() == 2:
+                prm.data.copy_(torch.randn(prm.shape, generator=gen, device=device) * 0.02)
+            else:
+                prm.data.fill_(0.0 if name.endswith("bias") else 1.0)
+
     def step(z, b=None):
+        if stack is not None:
+            return stack(z, mask_dev)
         b = bufs if b is None else b
         for tm in trimul:  # Pairformer order: triangle multiplication out, in, then the attention nodes
             z = tm(z, mask_dev, residual=True, buffers=b)
@@ -238,6 +256,9 @@ def run_ours(args) -> dict:
     launches_per_step = 6 + (1 if cfg["transition"] else 0) + 3 * len(trimul)
     flops_step = sum(2 * node_flops(L) + (transition_flops(L) if cfg["transition"] else 0.0)
                      + len(trimul) * trimul_flops(L, cfg["N"]) for L in lens)
+    if stack is not None:
+        launches_per_step *= cfg["blocks"]
+        flops_step *= cfg["blocks"]
 
     def barrier():
         if world > 1:
@@ -449,27 +470,6 @@ def run_sharded(args) -> dict:
     ms_median, ms_min = sorted(times)[len(times) // 2], min(times)
     if _lib.device_status() != 0:
         raise RuntimeError("a kernel abandoned a bounded wait during the benchmark")
-
-    # ---- the same step replayed from a CUDA graph (launch overhead removed; L2 not flushed) ------------------
-    graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream(device)
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        step(z_dev)
-        with torch.cuda.graph(graph, stream=side):
-            step(z_dev)
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    reps = max(10, min(args.steps, 50))
-    graph.replay()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        graph.replay()
-    e1.record()
-    e1.synchronize()
-    graph_ms = e0.elapsed_time(e1) / reps
-    del graph
 
     z_pin = z_rows.cpu().pin_memory()
     out_pin = torch.empty_like(z_pin).pin_memory()

@@ -65,6 +65,7 @@ class HostPipeline:
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.cmp_done[k])
                 dst.copy_(result, non_blocking=True)
+                result.record_stream(self.s_out)  # the copy-out reads it on this stream
                 self.out_done[k].record(self.s_out)
         for s in (self.s_in, self.s_cmp, self.s_out):
             start.wait_stream(s)

@@ -7,6 +7,7 @@ from .auto_chunk import (CHUNK_REGISTRY, PAIR_TRANSITION, TRIANGLE_ATTENTION, Ch
                          default_autochunk_min, iter_chunks)
 from .buffers import PreallocatedBuffers, ensure_buffer
 from .linear import Linear, WeightMode, WeightsLoadingConfig
+from .pairformer import PairformerNoSeqLayer, PairformerNoSeqModule
 from .transition import Transition
 from .triangle_multiplication import (TriangleMultiplicationMetadata, TriangleMultiplicationNode,
                                       TriangleMultiplicationNodeType, precompute_trimul_metadata,
@@ -22,5 +23,5 @@ __all__ = [
     "WeightMode", "WeightsLoadingConfig", "Transition", "TriangleAttention", "TriangleAttentionEndingNode",
     "TriangleAttentionNode", "TriangleAttentionNodeType", "TriangleAttentionStartingNode", "split_pair_bias_proj",
     "TriangleMultiplicationMetadata", "TriangleMultiplicationNode", "TriangleMultiplicationNodeType",
-    "precompute_trimul_metadata", "set_trimul_token_padding",
+    "precompute_trimul_metadata", "set_trimul_token_padding", "PairformerNoSeqLayer", "PairformerNoSeqModule",
 ]

@@ -190,3 +190,19 @@ def test_boltz_checkpoint_converters_feed_strict_loads():
     assert torch.equal(tr.fused_fc2_fc1.weight[512:].float(), ckpt[f"{p}.fc1.weight"].bfloat16().float())  # then gate rows
     with pytest.raises(ValueError):
         cu.get_transition_weights(ckpt, p, "t", dtype="int7")
+
+
+def test_pair_track_stack_has_the_reference_submodule_names():
+    """PairformerNoSeqModule / PairformerNoSeqLayer (bionemo_ir/_torch/layers/transformers/pairformer.py:255-363)."""
+    stack = b200.PairformerNoSeqModule(num_blocks=2, dtype=torch.bfloat16, trimul_high_precision=False, token_s=384,
+                                       num_heads=16)  # single-track arguments are accepted and unused
+    keys = set(stack.state_dict())
+    for i in range(2):
+        for sub in ("tri_mul_out.p_in.weight", "tri_mul_in.g_out.weight", "tri_attn_start.mha.in_proj.weight",
+                    "tri_attn_end.pair_bias_proj.weight", "transition_z.fused_fc2_fc1.weight", "transition_z.fc3.weight"):
+            assert f"layers.{i}.{sub}" in keys
+    layer = stack.layers[1]
+    assert layer.tri_mul_in.multiplication_type == b200.TriangleMultiplicationNodeType.INCOMING
+    assert layer.tri_attn_end.node_type == b200.TriangleAttentionNodeType.ENDING
+    assert layer.no_update_s and not layer.no_update_z
+    assert b200.PairformerNoSeqModule(num_blocks=0)(torch.zeros(1, 4, 4, 128), torch.ones(1, 4, 4)).shape == (1, 4, 4, 128)
