@@ -50,8 +50,16 @@ struct AttnParams {
   float* lse;
   float scale_log2;  // softmax_scale * log2(e)
   int empty_uniform;
+  int wide_store;  // out is 32-byte aligned and its strides are multiples of 16 elements
   int* status;
 };
+
+// 32-byte store; the address must be 32-byte aligned.
+__device__ __forceinline__ void stg256(void* p, const uint32_t* v) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+               "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
 
 // shared-memory map (bytes, relative to the 1024-aligned base)
 // K and the bias tiles are only read by the score MMAs, which run a tile ahead, so their ring frees early
@@ -550,9 +558,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       tc_fence_before();
       if (q < p.S) {
+        if (p.wide_store) {  // two full 32-byte sectors per row instead of four half sectors
+          stg256(out_row, pk);
+          stg256(out_row + 16, pk + 8);
+        } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          reinterpret_cast<uint4*>(out_row)[j] = make_uint4(pk[j * 4], pk[j * 4 + 1], pk[j * 4 + 2], pk[j * 4 + 3]);
+          for (int j = 0; j < 4; ++j)
+            reinterpret_cast<uint4*>(out_row)[j] = make_uint4(pk[j * 4], pk[j * 4 + 1], pk[j * 4 + 2], pk[j * 4 + 3]);
+        }
         if (p.lse)
           p.lse[((long long)it.br * p.S + q) * kHeads + it.h] =
               it.uniform ? -INFINITY : 0.6931471805599453f * (row_max * c + __log2f(row_sum));
@@ -649,6 +662,7 @@ int b200ta_attention(const void* q, const void* k, const void* v, const void* ga
   p.lse = lse;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.empty_uniform = empty_row_mode == B200TA_EMPTY_ROW_UNIFORM ? 1 : 0;
+  p.wide_store = (reinterpret_cast<uintptr_t>(out) & 31u) == 0 && os_br % 16 == 0 && os_s % 16 == 0 && os_h % 16 == 0;
   p.status = st->status_dev;
 
   B200TA_CHECK_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmDynamic));
