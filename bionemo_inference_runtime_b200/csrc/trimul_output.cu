@@ -21,7 +21,7 @@ constexpr int kTileM = 128;
 constexpr int kSmW = 0;                      // W_go' and W_po': 2 matrices x 2 K-halves x 128 rows x 128 B
 constexpr int kSmZ = kSmW + 65536;           // 2 stages x 32 KiB
 constexpr int kSmX = kSmZ + 2 * 32768;       // 2 stages x 32 KiB
-constexpr int kSmConst = kSmX + 2 * 32768;   // float4 [128] {c_gate, rowsum_p, c_p, 0}
+constexpr int kSmConst = kSmX + 2 * 32768;   // per channel pair: float4 [64] {c_gate0, c_gate1, rowsum_p0, rowsum_p1}, float2 [64] {c_p0, c_p1}
 constexpr int kSmStats = kSmConst + 2048;    // 2 stages x float4 [128] {rstd_o, -mean_o*rstd_o, mask, 0}
 constexpr int kSmXch = kSmStats + 2 * 2048;  // 2 x float4 [128] partial x statistics (alternating per tile)
 constexpr int kSmBars = kSmXch + 2 * 2048;
@@ -80,9 +80,11 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
     fence_mbar_init();
   }
   // per-channel constants of the epilogue
-  if (threadIdx.x < kC) {
-    const float2 g = p.sc[threadIdx.x], q = p.sc[kC + threadIdx.x];
-    reinterpret_cast<float4*>(gen + kSmConst)[threadIdx.x] = make_float4(g.y, q.x, q.y, 0.f);
+  if (threadIdx.x < kC / 2) {
+    const int c = 2 * threadIdx.x;
+    const float2 g0 = p.sc[c], g1 = p.sc[c + 1], q0 = p.sc[kC + c], q1 = p.sc[kC + c + 1];
+    reinterpret_cast<float4*>(gen + kSmConst)[threadIdx.x] = make_float4(g0.y, g1.y, q0.x, q1.x);
+    reinterpret_cast<float2*>(gen + kSmConst + 1024)[threadIdx.x] = make_float2(q0.y, q1.y);
   }
   if (warp == 13) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
   tc_fence_before();
@@ -252,7 +254,8 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
     const int e = warp >> 2;
     const int m = (warp & 3) * 32 + lane;
     const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
-    const float4* c4 = reinterpret_cast<const float4*>(gen + kSmConst);
+    const float4* c4 = reinterpret_cast<const float4*>(gen + kSmConst);         // per channel pair
+    const float2* c2 = reinterpret_cast<const float2*>(gen + kSmConst + 1024);  // per channel pair
     bool ok = true;
     for (int it = 0; ok && it < my_tiles; ++it) {
       const int tile = blockIdx.x + it * gridDim.x;
@@ -282,7 +285,8 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
       if (!ok) break;
       tc_fence_after();
       const float4 stv = reinterpret_cast<const float4*>(gen + kSmStats + stage * 2048)[m];
-      const float rstd = stv.x, nmr = stv.y, mval = stv.z;
+      const uint64_t rstd2 = pack_f32x2(stv.x, stv.x), nmr2 = pack_f32x2(stv.y, stv.y), mval2 = pack_f32x2(stv.z, stv.z);
+      const uint64_t half2 = pack_f32x2(0.5f, 0.5f);
       // four chunks of 16 output channels: [32 g + 16 h, +16) for this warpgroup's groups g = e, e + 2; the TMEM
       // loads of the next chunk are in flight while this one is computed
       uint32_t ag[2][16], ap[2][16];
@@ -304,14 +308,21 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
         uint32_t packed[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const float4 k0 = c4[ch0 + 2 * c], k1 = c4[ch0 + 2 * c + 1];  // {c_gate, rowsum_p, c_p}
+          // two channels at a time, packed fp32x2 math; constants per channel pair: {c_gate0, c_gate1, rowsum0,
+          // rowsum1} and {c_p0, c_p1}
+          const float4 ka = c4[(ch0 >> 1) + c];
+          const float2 kb = c2[(ch0 >> 1) + c];
+          float a0, a1;
+          unpack_f32x2(add_f32x2(pack_f32x2(__uint_as_float(xg[2 * c]), __uint_as_float(xg[2 * c + 1])), pack_f32x2(ka.x, ka.y)),
+                       a0, a1);
           // gate rows are pre-halved: sigmoid(x) = 0.5 * tanh(x / 2) + 0.5
-          const float s0 = fmaf(0.5f, tanh_approx(__uint_as_float(xg[2 * c]) + k0.x), 0.5f);
-          const float s1 = fmaf(0.5f, tanh_approx(__uint_as_float(xg[2 * c + 1]) + k1.x), 0.5f);
-          const float v0 = fmaf(rstd, __uint_as_float(xp[2 * c]), fmaf(nmr, k0.y, k0.z));
-          const float v1 = fmaf(rstd, __uint_as_float(xp[2 * c + 1]), fmaf(nmr, k1.y, k1.z));
+          const uint64_t s2 = fma_f32x2(pack_f32x2(tanh_approx(a0), tanh_approx(a1)), half2, half2);
+          const uint64_t v2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xp[2 * c]), __uint_as_float(xp[2 * c + 1])),
+                                        fma_f32x2(nmr2, pack_f32x2(ka.z, ka.w), pack_f32x2(kb.x, kb.y)));
           const uint32_t r = res[ck >> 1][h * 8 + c];
-          packed[c] = pack_bf16x2(fmaf(s0, v0, bf16_lo(r)) * mval, fmaf(s1, v1, bf16_hi(r)) * mval);
+          float o0, o1;
+          unpack_f32x2(mul_f32x2(fma_f32x2(s2, v2, pack_f32x2(bf16_lo(r), bf16_hi(r))), mval2), o0, o1);
+          packed[c] = pack_bf16x2(o0, o1);
         }
         if (j < p.N) stg256(p.out + b * p.os_b + i * p.os_i + (long long)j * p.os_j + ch0, packed);
       }

@@ -27,9 +27,9 @@ constexpr int kTileM = 128;                 // positions per tile
 constexpr int kSmW = 0;                     // folded rows: 2 halves (64 channels of K each) x 512 rows x 128 B
 constexpr int kWHalf = kTriInRows * 128;    // 64 KiB
 constexpr int kSmZ = kSmW + 2 * kWHalf;     // 2 stages x 32 KiB
-constexpr int kSmMask = kSmZ + 2 * 32768;   // 2 stages x 128 floats
-constexpr int kSmBars = kSmMask + 2 * 512;
-enum Bar { W_FULL = 0, Z_FULL = 1, Z_READY = 3, Z_EMPTY = 5, ACC_FULL = 7, ACC_EMPTY = 11, NUM_BARS = 15 };
+constexpr int kSmMask = kSmZ + 2 * 32768;   // 4 slots x 128 floats (tile i uses slot i & 3)
+constexpr int kSmBars = kSmMask + 4 * 512;
+enum Bar { W_FULL = 0, Z_FULL = 1, Z_READY = 3, Z_EMPTY = 5, ACC_FULL = 7, ACC_EMPTY = 9, NUM_BARS = 11 };
 constexpr int kSmTotal = kSmBars + 256;
 constexpr int kSmDynamic = kSmTotal + 1024;
 
@@ -69,10 +69,8 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + (Z_FULL + i) * 8, 1);
       mbar_init(bars + (Z_READY + i) * 8, 4);   // the four normaliser warps
-      mbar_init(bars + (Z_EMPTY + i) * 8, 9);   // the MMA commit + the eight epilogue warps (they read the mask)
-    }
-    for (int i = 0; i < 4; ++i) {  // per (warpgroup, half of the tile's positions)
-      mbar_init(bars + (ACC_FULL + i) * 8, 1);
+      mbar_init(bars + (Z_EMPTY + i) * 8, 1);   // the MMA commit: the tile can be reloaded once the MMAs have read it
+      mbar_init(bars + (ACC_FULL + i) * 8, 1);  // per warpgroup
       mbar_init(bars + (ACC_EMPTY + i) * 8, 4);
     }
     fence_mbar_init();
@@ -114,38 +112,33 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
   } else if (warp == 13) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // Each accumulator covers 64 of the tile's 128 positions, so that the MMAs of one half overlap the epilogue
-      // of the other: TMEM columns (warpgroup, half, gate | value) x 64.
-      constexpr uint32_t idesc = make_idesc_bf16(128, kTileM / 2);
+      constexpr uint32_t idesc = make_idesc_bf16(128, kTileM);
       bool ok = mbar_wait(bars + W_FULL * 8, 0, abort_flag);
       for (int i = 0; ok && i < my_tiles; ++i) {
         const int stage = i & 1;
         ok = mbar_wait(bars + (Z_READY + stage) * 8, (i >> 1) & 1, abort_flag);
         if (!ok) break;
-        for (int half = 0; ok && half < 2; ++half) {
-          // rows 64 half .. of the [128 positions][64 channels] blocks: 8 KiB further
-          const uint64_t dz = make_smem_desc(base + kSmZ + stage * 32768 + half * 8192, 16, 1024, kLayoutSw128);
-          for (int wg = 0; ok && wg < 2; ++wg) {
-            ok = mbar_wait(bars + (ACC_EMPTY + wg * 2 + half) * 8, (i & 1) ^ 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
+        const uint64_t dz = make_smem_desc(base + kSmZ + stage * 32768, 16, 1024, kLayoutSw128);
+        for (int wg = 0; ok && wg < 2; ++wg) {
+          ok = mbar_wait(bars + (ACC_EMPTY + wg) * 8, (i & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-            for (int acc = 0; acc < 2; ++acc) {  // gate rows, then value rows of this warpgroup's channels
-              const uint32_t d = tmem_base + (wg * 2 + half) * 128 + acc * 64;
-              const uint64_t dw = make_smem_desc(base + kSmW + (wg * 2 + acc) * 128 * 128, 16, 1024, kLayoutSw128);
+          for (int acc = 0; acc < 2; ++acc) {  // gate rows, then value rows of this warpgroup's channels
+            const uint32_t d = tmem_base + (wg * 2 + acc) * 128;
+            const uint64_t dw = make_smem_desc(base + kSmW + (wg * 2 + acc) * 128 * 128, 16, 1024, kLayoutSw128);
 #pragma unroll
-              for (int k = 0; k < 8; ++k)
-                umma_ss(d, dw + ((k >> 2) * (kWHalf >> 4) + (k & 3) * 2), dz + ((k >> 2) * (16384 >> 4) + (k & 3) * 2),
-                        idesc, k > 0 ? 1u : 0u);
-            }
-            umma_commit(bars + (ACC_FULL + wg * 2 + half) * 8);
+            for (int k = 0; k < 8; ++k)
+              umma_ss(d, dw + ((k >> 2) * (kWHalf >> 4) + (k & 3) * 2), dz + ((k >> 2) * (16384 >> 4) + (k & 3) * 2), idesc,
+                      k > 0 ? 1u : 0u);
           }
+          umma_commit(bars + (ACC_FULL + wg) * 8);
         }
         if (!ok) break;
         umma_commit(bars + (Z_EMPTY + stage) * 8);
       }
     }
-  } else if (warp >= 8) {
+  } else if (warp >= 8 && warp < 12) {
     // ------------------------------------------------------------------ normaliser: one thread per position
     const int m = (warp - 8) * 32 + lane;
     bool ok = true;
@@ -160,10 +153,10 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       ok = mbar_wait(bars + (Z_FULL + stage) * 8, (i >> 1) & 1, abort_flag);
       if (!ok) break;
       const uint32_t z0 = base + kSmZ + stage * 32768;
-      // three passes over the row in shared memory (sum, squared deviations, write-back) keep the register
-      // footprint small; the row is 256 bytes and the reads are conflict-free
+      // Three passes over the 256-byte row in shared memory (sum, squared deviations, write-back), eight 16-byte
+      // loads in flight at a time: keeps the register footprint small; the reads are conflict-free.
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
+#pragma unroll 8
       for (int c = 0; c < 16; ++c) {
         const uint4 x = lds128(z0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
         sum4[0] += bf16_lo(x.x) + bf16_hi(x.x);
@@ -173,7 +166,7 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       }
       const float mu = ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3])) * (1.f / kC);
       float var4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
+#pragma unroll 8
       for (int c = 0; c < 16; ++c) {
         const uint4 x = lds128(z0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
         const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
@@ -186,7 +179,7 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       }
       const float rstd = rsqrtf(((var4[0] + var4[1]) + (var4[2] + var4[3])) * (1.f / kC) + p.eps);
       const float nmr = -mu * rstd;
-#pragma unroll 4
+#pragma unroll 8
       for (int c = 0; c < 16; ++c) {
         const uint32_t addr = z0 + (c >> 3) * 16384 + sw128_offset(m, c & 7);
         uint4 x = lds128(addr);
@@ -196,17 +189,21 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
         x.w = pack_bf16x2(fmaf(bf16_lo(x.w), rstd, nmr), fmaf(bf16_hi(x.w), rstd, nmr));
         sts128(addr, x);
       }
-      reinterpret_cast<float*>(gen + kSmMask + stage * 512)[m] = mval;
+      // The mask values have their own four slots: the epilogue of a tile runs while its z stage is already being
+      // reloaded.  A slot is rewritten three tiles later, when that epilogue is long done (the MMAs of tile t + 1
+      // wait for the accumulators of tile t, and this write for tile t + 3 waits for the MMAs of tile t + 1).
+      reinterpret_cast<float*>(gen + kSmMask + (i & 3) * 512)[m] = mval;
       fence_proxy_async_smem();  // the MMA reads the tile through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + (Z_READY + stage) * 8);
     }
-  } else {
+  } else if (warp < 8) {
     // ------------------------------------------------------------------ epilogue warps: one thread per channel
     const int wg = warp >> 2;
     const int ch = (warp & 3) * 32 + lane;  // channel inside this warpgroup's 128 == TMEM lane
     const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + wg * 256;
     const float cg = p.sc[wg * 256 + ch].y, cp = p.sc[wg * 256 + 128 + ch].y;
+    const uint64_t cg2 = pack_f32x2(cg, cg), cp2 = pack_f32x2(cp, cp);
     bool ok = true;
     for (int i = 0; ok && i < my_tiles; ++i) {
       const int tile = blockIdx.x + i * gridDim.x;
@@ -214,54 +211,57 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       const int r = br % p.R, b = br / p.R;
       const int stage = i & 1;
       const float bscale = (wg == 1 && p.b_scale) ? __ldg(p.b_scale + b) : 1.f;
-      const float4* mk = reinterpret_cast<const float4*>(gen + kSmMask + stage * 512);
+      const uint64_t hs2 = pack_f32x2(0.5f * bscale, 0.5f * bscale);
+      const float4* mk = reinterpret_cast<const float4*>(gen + kSmMask + (i & 3) * 512);
       __nv_bfloat16* dst = p.ab + ((long long)(b * 2 + wg) * kTriHidden + ch) * p.R * p.pitch + (long long)r * p.pitch +
                            st * kTileM;
+      ok = mbar_wait(bars + (ACC_FULL + wg) * 8, i & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        ok = mbar_wait(bars + (ACC_FULL + wg * 2 + half) * 8, i & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t acc = lane_taddr + half * 128;  // gate columns, the value columns follow 64 further
+        const uint32_t acc = lane_taddr + half * 64;  // gate columns of these 64 positions; the value columns lie 128 further
         // 16 positions at a time; the TMEM loads of the next chunk are in flight while this one is computed
         uint32_t g[2][16], v[2][16];
         tmem_ld16(acc, g[0]);
-        tmem_ld16(acc + 64, v[0]);
+        tmem_ld16(acc + 128, v[0]);
 #pragma unroll
         for (int part = 0; part < 4; ++part) {
           const int pos0 = half * 64 + part * 16;
-          float mv[16];
+          // per position: half of mask (* b scale); sigmoid(g) * v * m = (tanh(g/2) * h + h) with h = v * m / 2
+          uint64_t mh2[8];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float4 t = mk[(pos0 >> 2) + j];
-            mv[4 * j] = t.x * bscale, mv[4 * j + 1] = t.y * bscale, mv[4 * j + 2] = t.z * bscale, mv[4 * j + 3] = t.w * bscale;
+            mh2[2 * j] = mul_f32x2(pack_f32x2(t.x, t.y), hs2);
+            mh2[2 * j + 1] = mul_f32x2(pack_f32x2(t.z, t.w), hs2);
           }
           tmem_ld_wait();
           if (part + 1 < 4) {
             tmem_ld16(acc + (part + 1) * 16, g[(part + 1) & 1]);
-            tmem_ld16(acc + 64 + (part + 1) * 16, v[(part + 1) & 1]);
+            tmem_ld16(acc + 128 + (part + 1) * 16, v[(part + 1) & 1]);
           }
           const uint32_t (&gg)[16] = g[part & 1];
           const uint32_t (&vv)[16] = v[part & 1];
           uint32_t packed[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            // gate rows are pre-halved: sigmoid(x) = 0.5 * tanh(x / 2) + 0.5
-            const float s0 = fmaf(0.5f, tanh_approx(__uint_as_float(gg[2 * j]) + cg), 0.5f);
-            const float s1 = fmaf(0.5f, tanh_approx(__uint_as_float(gg[2 * j + 1]) + cg), 0.5f);
-            const float o0 = s0 * (__uint_as_float(vv[2 * j]) + cp) * mv[2 * j];
-            const float o1 = s1 * (__uint_as_float(vv[2 * j + 1]) + cp) * mv[2 * j + 1];
+            // packed fp32x2 math on two positions; gate rows are pre-halved
+            float a0, a1;
+            unpack_f32x2(add_f32x2(pack_f32x2(__uint_as_float(gg[2 * j]), __uint_as_float(gg[2 * j + 1])), cg2), a0, a1);
+            const uint64_t h2 = mul_f32x2(add_f32x2(pack_f32x2(__uint_as_float(vv[2 * j]), __uint_as_float(vv[2 * j + 1])), cp2),
+                                          mh2[j]);
+            float o0, o1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(tanh_approx(a0), tanh_approx(a1)), h2, h2), o0, o1);
             packed[j] = pack_bf16x2(o0, o1);
           }
           if (st * kTileM + pos0 + 16 <= p.pitch) stg256(dst + pos0, packed);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars + (ACC_EMPTY + wg * 2 + half) * 8);
       }
-      if (!ok) break;
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars + (Z_EMPTY + stage) * 8);  // done with this stage's mask values
+      if (lane == 0) mbar_arrive(bars + (ACC_EMPTY + wg) * 8);
+      if (!ok) break;
     }
   }
 
