@@ -2,13 +2,14 @@
 //   out[b,i,j,:] = sigmoid(LN_in(z[b,i,j,:])·W_goᵀ + b_go) ⊙ (LN_out(x[b,:,i,j])·W_poᵀ + b_po)   [+ z]   [* mask]
 // x is the contraction result, channel-major x[b][d][i][j] (bf16).  One tile = 128 consecutive positions j of one
 // pair row (b, i); per tile two tcgen05 GEMMs share one accumulator slot (256 TMEM columns, double-buffered):
-//   D_g[pos, ch] = ẑ[pos, :] · W_go'[ch, :]ᵀ   A = the z tile, normalised in shared memory (K-major)
+//   D_g[pos, ch] = z[pos, :] · W_go'[ch, :]ᵀ    A = the raw z tile (K-major)
 //   D_p[pos, ch] = x[:, pos]ᵀ · W_po'[ch, :]ᵀ   A = the x tile as it lies in memory, [d][pos] = MN-major
-// LN_out is folded into W_po' (rows centred, per-row sum kept): the epilogue applies
-// rstd·(D_p − mean·rowsum) + const with the per-position statistics the normaliser warps compute from the x tile.
+// Both LayerNorms are folded into the weights (rows centred, per-row sum kept): the epilogue, one thread per
+// position, applies rstd·(D − mean·rowsum) + const with the statistics the statistics warps computed from the two
+// tiles while the MMAs ran - neither tile is rewritten and the MMAs wait for nothing but the loads.
 //
 // Warp roles (448 threads): warps 0-7 epilogue (thread = position; the two warpgroups take alternate groups of 32
-// output channels), warps 8-11 normaliser (z rows: one thread per position; x columns: a thread takes two
+// output channels), warps 8-11 statistics (z rows: one thread per position; x columns: a thread takes two
 // neighbouring positions over half of the channels), warp 12 TMA producer, warp 13 MMA issuer / TMEM owner.
 #include "common.cuh"
 #include "layout.h"
@@ -21,11 +22,12 @@ constexpr int kTileM = 128;
 constexpr int kSmW = 0;                      // W_go' and W_po': 2 matrices x 2 K-halves x 128 rows x 128 B
 constexpr int kSmZ = kSmW + 65536;           // 2 stages x 32 KiB
 constexpr int kSmX = kSmZ + 2 * 32768;       // 2 stages x 32 KiB
-constexpr int kSmConst = kSmX + 2 * 32768;   // per channel pair: float4 [64] {c_gate0, c_gate1, rowsum_p0, rowsum_p1}, float2 [64] {c_p0, c_p1}
-constexpr int kSmStats = kSmConst + 2048;    // 2 stages x float4 [128] {rstd_o, -mean_o*rstd_o, mask, 0}
-constexpr int kSmXch = kSmStats + 2 * 2048;  // 2 x float4 [128] partial x statistics (alternating per tile)
+constexpr int kSmConst = kSmX + 2 * 32768;   // per channel pair: float4 [64] {c_gate0, c_gate1, rowsum_g0, rowsum_g1}, float4 [64] {c_p0, c_p1, rowsum_p0, rowsum_p1}
+constexpr int kSmStats = kSmConst + 2048;    // 4 slots (tile i uses slot i & 3) x { float4 [128] {rstd_o, -mean_o*rstd_o, rstd_i, -mean_i*rstd_i}, float [128] mask }
+constexpr int kStatsSlot = 2048 + 512;
+constexpr int kSmXch = kSmStats + 4 * kStatsSlot;  // 2 x float4 [128] partial x statistics (alternating per tile)
 constexpr int kSmBars = kSmXch + 2 * 2048;
-enum Bar { W_FULL = 0, IN_FULL = 1, READY = 3, IN_EMPTY = 5, ACC_FULL = 7, ACC_EMPTY = 9, XCH = 11, NUM_BARS = 12 };
+enum Bar { W_FULL = 0, IN_FULL = 1, READY = 3, IN_EMPTY = 7, ACC_FULL = 9, ACC_EMPTY = 11, XCH = 13, NUM_BARS = 14 };
 constexpr int kSmTotal = kSmBars + 256;
 constexpr int kSmDynamic = kSmTotal + 1024;
 
@@ -70,10 +72,12 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
     abort_flag[0] = 0, abort_flag[1] = 0;
     mbar_init(bars + W_FULL * 8, 1);
     mbar_init(bars + XCH * 8, 4);
+    // statistics written (the four statistics warps): one barrier per statistics slot, because the statistics of
+    // tile t + 2 may be complete before the epilogue of tile t has looked at its barrier
+    for (int i = 0; i < 4; ++i) mbar_init(bars + (READY + i) * 8, 4);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + (IN_FULL + i) * 8, 1);
-      mbar_init(bars + (READY + i) * 8, 4);     // the four normaliser warps
-      mbar_init(bars + (IN_EMPTY + i) * 8, 9);  // the MMA commit + the eight epilogue warps (statistics, mask)
+      mbar_init(bars + (IN_EMPTY + i) * 8, 5);  // the MMA commit + the four statistics warps have read the tiles
       mbar_init(bars + (ACC_FULL + i) * 8, 1);
       mbar_init(bars + (ACC_EMPTY + i) * 8, 8);
     }
@@ -83,8 +87,8 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
   if (threadIdx.x < kC / 2) {
     const int c = 2 * threadIdx.x;
     const float2 g0 = p.sc[c], g1 = p.sc[c + 1], q0 = p.sc[kC + c], q1 = p.sc[kC + c + 1];
-    reinterpret_cast<float4*>(gen + kSmConst)[threadIdx.x] = make_float4(g0.y, g1.y, q0.x, q1.x);
-    reinterpret_cast<float2*>(gen + kSmConst + 1024)[threadIdx.x] = make_float2(q0.y, q1.y);
+    reinterpret_cast<float4*>(gen + kSmConst)[threadIdx.x] = make_float4(g0.y, g1.y, g0.x, g1.x);
+    reinterpret_cast<float4*>(gen + kSmConst + 1024)[threadIdx.x] = make_float4(q0.y, q1.y, q0.x, q1.x);
   }
   if (warp == 13) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
   tc_fence_before();
@@ -131,7 +135,7 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
       bool ok = mbar_wait(bars + W_FULL * 8, 0, abort_flag);
       for (int it = 0; ok && it < my_tiles; ++it) {
         const int stage = it & 1, slot = it & 1;
-        ok = mbar_wait(bars + (READY + stage) * 8, (it >> 1) & 1, abort_flag);
+        ok = mbar_wait(bars + (IN_FULL + stage) * 8, (it >> 1) & 1, abort_flag);
         ok = ok && mbar_wait(bars + (ACC_EMPTY + slot) * 8, ((it >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
@@ -168,11 +172,12 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
       if (p.mask != nullptr) mval = j < p.N ? __ldg(p.mask + b * p.ms_b + i * p.ms_i + (long long)j * p.ms_j) : 0.f;
       ok = mbar_wait(bars + (IN_FULL + stage) * 8, (it >> 1) & 1, abort_flag);
       if (!ok) break;
-      // ---- z row t: LayerNorm in place (three passes keep the register footprint small)
+      // ---- z row t: mean and variance (two passes over the row in shared memory; nothing is written back)
+      float rstd_i, nmr_i;
       {
         const uint32_t z0 = base + kSmZ + stage * 32768;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
+#pragma unroll 8
         for (int c = 0; c < 16; ++c) {
           const uint4 x = lds128(z0 + (c >> 3) * 16384 + sw128_offset(t, c & 7));
           sum4[0] += bf16_lo(x.x) + bf16_hi(x.x);
@@ -182,7 +187,7 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
         }
         const float mu = ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3])) * (1.f / kC);
         float var4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
+#pragma unroll 8
         for (int c = 0; c < 16; ++c) {
           const uint4 x = lds128(z0 + (c >> 3) * 16384 + sw128_offset(t, c & 7));
           const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
@@ -193,18 +198,8 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
             var4[e] = fmaf(d1, d1, var4[e]);
           }
         }
-        const float rstd = rsqrtf(((var4[0] + var4[1]) + (var4[2] + var4[3])) * (1.f / kC) + p.eps);
-        const float nmr = -mu * rstd;
-#pragma unroll 4
-        for (int c = 0; c < 16; ++c) {
-          const uint32_t addr = z0 + (c >> 3) * 16384 + sw128_offset(t, c & 7);
-          uint4 x = lds128(addr);
-          x.x = pack_bf16x2(fmaf(bf16_lo(x.x), rstd, nmr), fmaf(bf16_hi(x.x), rstd, nmr));
-          x.y = pack_bf16x2(fmaf(bf16_lo(x.y), rstd, nmr), fmaf(bf16_hi(x.y), rstd, nmr));
-          x.z = pack_bf16x2(fmaf(bf16_lo(x.z), rstd, nmr), fmaf(bf16_hi(x.z), rstd, nmr));
-          x.w = pack_bf16x2(fmaf(bf16_lo(x.w), rstd, nmr), fmaf(bf16_hi(x.w), rstd, nmr));
-          sts128(addr, x);
-        }
+        rstd_i = rsqrtf(((var4[0] + var4[1]) + (var4[2] + var4[3])) * (1.f / kC) + p.eps);
+        nmr_i = -mu * rstd_i;
       }
       // ---- x columns: this thread takes positions 2q, 2q+1 over channels [64 h, 64 h + 64)
       {
@@ -243,11 +238,17 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
         const float mean = 0.5f * (ma + mc);
         const float var = (qa + qc + (ma - mc) * (ma - mc) * 32.f) * (1.f / kTriHidden);
         const float rstd = rsqrtf(var + p.eps);
-        reinterpret_cast<float4*>(gen + kSmStats + stage * 2048)[t] = make_float4(rstd, -mean * rstd, mval, 0.f);
+        // Statistics and mask go to one of four slots: the epilogue of a tile may still read its slot while the
+        // next two tiles' statistics are written (the stage itself is handed back below, before the epilogue ran).
+        uint8_t* slot = gen + kSmStats + (it & 3) * kStatsSlot;
+        reinterpret_cast<float4*>(slot)[t] = make_float4(rstd, -mean * rstd, rstd_i, nmr_i);
+        reinterpret_cast<float*>(slot + 2048)[t] = mval;
       }
-      fence_proxy_async_smem();  // the MMA reads the normalised z tile through the async proxy
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars + (READY + stage) * 8);
+      if (lane == 0) {
+        mbar_arrive(bars + (READY + (it & 3)) * 8);
+        mbar_arrive(bars + (IN_EMPTY + stage) * 8);  // done reading the two tiles
+      }
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps: one thread per position
@@ -255,7 +256,7 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
     const int m = (warp & 3) * 32 + lane;
     const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     const float4* c4 = reinterpret_cast<const float4*>(gen + kSmConst);         // per channel pair
-    const float2* c2 = reinterpret_cast<const float2*>(gen + kSmConst + 1024);  // per channel pair
+    const float4* c4b = reinterpret_cast<const float4*>(gen + kSmConst + 1024);  // per channel pair
     bool ok = true;
     for (int it = 0; ok && it < my_tiles; ++it) {
       const int tile = blockIdx.x + it * gridDim.x;
@@ -281,11 +282,15 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
           for (int c = 0; c < 16; ++c) res[gi][c] = 0u;
         }
       }
-      ok = mbar_wait(bars + (ACC_FULL + slot) * 8, (it >> 1) & 1, abort_flag);
+      ok = mbar_wait(bars + (READY + (it & 3)) * 8, (it >> 2) & 1, abort_flag) &&
+           mbar_wait(bars + (ACC_FULL + slot) * 8, (it >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const float4 stv = reinterpret_cast<const float4*>(gen + kSmStats + stage * 2048)[m];
-      const uint64_t rstd2 = pack_f32x2(stv.x, stv.x), nmr2 = pack_f32x2(stv.y, stv.y), mval2 = pack_f32x2(stv.z, stv.z);
+      const uint8_t* stats = gen + kSmStats + (it & 3) * kStatsSlot;
+      const float4 stv = reinterpret_cast<const float4*>(stats)[m];
+      const float mval = reinterpret_cast<const float*>(stats + 2048)[m];
+      const uint64_t rstd2 = pack_f32x2(stv.x, stv.x), nmr2 = pack_f32x2(stv.y, stv.y), mval2 = pack_f32x2(mval, mval);
+      const uint64_t rstdg2 = pack_f32x2(stv.z, stv.z), nmrg2 = pack_f32x2(stv.w, stv.w);
       const uint64_t half2 = pack_f32x2(0.5f, 0.5f);
       // four chunks of 16 output channels: [32 g + 16 h, +16) for this warpgroup's groups g = e, e + 2; the TMEM
       // loads of the next chunk are in flight while this one is computed
@@ -308,17 +313,18 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
         uint32_t packed[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          // two channels at a time, packed fp32x2 math; constants per channel pair: {c_gate0, c_gate1, rowsum0,
-          // rowsum1} and {c_p0, c_p1}
+          // two channels at a time, packed fp32x2 math; constants per channel pair: {const0, const1, rowsum0,
+          // rowsum1} of the gate rows and of the projection rows
           const float4 ka = c4[(ch0 >> 1) + c];
-          const float2 kb = c2[(ch0 >> 1) + c];
+          const float4 kb = c4b[(ch0 >> 1) + c];
           float a0, a1;
-          unpack_f32x2(add_f32x2(pack_f32x2(__uint_as_float(xg[2 * c]), __uint_as_float(xg[2 * c + 1])), pack_f32x2(ka.x, ka.y)),
+          unpack_f32x2(fma_f32x2(rstdg2, pack_f32x2(__uint_as_float(xg[2 * c]), __uint_as_float(xg[2 * c + 1])),
+                                 fma_f32x2(nmrg2, pack_f32x2(ka.z, ka.w), pack_f32x2(ka.x, ka.y))),
                        a0, a1);
           // gate rows are pre-halved: sigmoid(x) = 0.5 * tanh(x / 2) + 0.5
           const uint64_t s2 = fma_f32x2(pack_f32x2(tanh_approx(a0), tanh_approx(a1)), half2, half2);
           const uint64_t v2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xp[2 * c]), __uint_as_float(xp[2 * c + 1])),
-                                        fma_f32x2(nmr2, pack_f32x2(ka.z, ka.w), pack_f32x2(kb.x, kb.y)));
+                                        fma_f32x2(nmr2, pack_f32x2(kb.z, kb.w), pack_f32x2(kb.x, kb.y)));
           const uint32_t r = res[ck >> 1][h * 8 + c];
           float o0, o1;
           unpack_f32x2(mul_f32x2(fma_f32x2(s2, v2, pack_f32x2(bf16_lo(r), bf16_hi(r))), mval2), o0, o1);
@@ -328,10 +334,7 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bars + (ACC_EMPTY + slot) * 8);
-        mbar_arrive(bars + (IN_EMPTY + stage) * 8);  // done with this stage's statistics
-      }
+      if (lane == 0) mbar_arrive(bars + (ACC_EMPTY + slot) * 8);
     }
   }
 

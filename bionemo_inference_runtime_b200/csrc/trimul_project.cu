@@ -1,5 +1,5 @@
 // Triangle-multiplication input stage for sm_100a:
-//   x̂        = LayerNorm_in(z)                       (bf16, as the eager module rounds it)
+//   x̂        = LayerNorm_in(z)
 //   ab[ch]   = sigmoid(x̂·W_g[ch] + b_g) * (x̂·W_p[ch] + b_p) * mask          ch = a(0..127) | b(128..255)
 // written channel-major, ab[b][ch][r][s], so that the contraction kernel finds the index it sums over (s)
 // contiguous.  The incoming node calls this with the pair strides swapped (rows r = pair columns).
@@ -10,11 +10,11 @@
 // contiguous 256-byte run of the channel-major output.  Per tile four such products: gate and value of the a
 // channels (warpgroup 0 finishes them) and of the b channels (warpgroup 1).
 //
-// LayerNorm is applied to the tile in shared memory before the MMA (one thread per position: statistics in fp32,
-// x̂ written back as bf16 over the raw values); gamma is folded into the weight rows, beta and the biases into a
-// per-channel constant.
+// LayerNorm is folded into the weights (rows centred, per-row sum kept; gamma, beta and the biases included): the
+// MMAs run on the raw tile as soon as it has landed, four statistics warps (one thread per position) compute mean
+// and rstd of every position meanwhile, and the epilogue applies rstd[pos]·(D − mean[pos]·rowsum[ch]) + const[ch].
 //
-// Warp roles (448 threads): warps 0-3 epilogue of the a channels, 4-7 of the b channels, 8-11 normaliser,
+// Warp roles (448 threads): warps 0-3 epilogue of the a channels, 4-7 of the b channels, 8-11 statistics,
 // warp 12 TMA producer, warp 13 MMA issuer / TMEM owner.
 #include "common.cuh"
 #include "layout.h"
@@ -27,16 +27,17 @@ constexpr int kTileM = 128;                 // positions per tile
 constexpr int kSmW = 0;                     // folded rows: 2 halves (64 channels of K each) x 512 rows x 128 B
 constexpr int kWHalf = kTriInRows * 128;    // 64 KiB
 constexpr int kSmZ = kSmW + 2 * kWHalf;     // 2 stages x 32 KiB
-constexpr int kSmMask = kSmZ + 2 * 32768;   // 4 slots x 128 floats (tile i uses slot i & 3)
-constexpr int kSmBars = kSmMask + 4 * 512;
-enum Bar { W_FULL = 0, Z_FULL = 1, Z_READY = 3, Z_EMPTY = 5, ACC_FULL = 7, ACC_EMPTY = 9, NUM_BARS = 11 };
+constexpr int kSmStats = kSmZ + 2 * 32768;  // 4 slots (tile i uses slot i & 3) x 3 x 128 floats: rstd, -mean*rstd, mask/2
+constexpr int kStatsSlot = 3 * 512;
+constexpr int kSmBars = kSmStats + 4 * kStatsSlot;
+enum Bar { W_FULL = 0, Z_FULL = 1, STATS_READY = 3, Z_EMPTY = 7, ACC_FULL = 9, ACC_EMPTY = 11, NUM_BARS = 13 };
 constexpr int kSmTotal = kSmBars + 256;
 constexpr int kSmDynamic = kSmTotal + 1024;
 
 struct ProjectParams {
   int B, R, S;
   int tiles_s, num_tiles;
-  const float2* sc;  // {rowsum, const} per folded row; only the constant is used here
+  const float2* sc;  // {rowsum, const} per folded row
   float eps;
   const float* mask;  // may be NULL
   long long ms_b, ms_r, ms_s;
@@ -68,11 +69,13 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
     mbar_init(bars + W_FULL * 8, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + (Z_FULL + i) * 8, 1);
-      mbar_init(bars + (Z_READY + i) * 8, 4);   // the four normaliser warps
-      mbar_init(bars + (Z_EMPTY + i) * 8, 1);   // the MMA commit: the tile can be reloaded once the MMAs have read it
+      mbar_init(bars + (Z_EMPTY + i) * 8, 5);   // the MMA commit + the four statistics warps have read the tile
       mbar_init(bars + (ACC_FULL + i) * 8, 1);  // per warpgroup
       mbar_init(bars + (ACC_EMPTY + i) * 8, 4);
     }
+    // statistics of a tile written (the four statistics warps): one barrier per statistics slot, because the
+    // statistics of tile t + 2 may be complete before the epilogue of tile t has looked at its barrier
+    for (int i = 0; i < 4; ++i) mbar_init(bars + (STATS_READY + i) * 8, 4);
     fence_mbar_init();
   }
   if (warp == 13) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -116,7 +119,7 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       bool ok = mbar_wait(bars + W_FULL * 8, 0, abort_flag);
       for (int i = 0; ok && i < my_tiles; ++i) {
         const int stage = i & 1;
-        ok = mbar_wait(bars + (Z_READY + stage) * 8, (i >> 1) & 1, abort_flag);
+        ok = mbar_wait(bars + (Z_FULL + stage) * 8, (i >> 1) & 1, abort_flag);
         if (!ok) break;
         const uint64_t dz = make_smem_desc(base + kSmZ + stage * 32768, 16, 1024, kLayoutSw128);
         for (int wg = 0; ok && wg < 2; ++wg) {
@@ -139,7 +142,7 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       }
     }
   } else if (warp >= 8 && warp < 12) {
-    // ------------------------------------------------------------------ normaliser: one thread per position
+    // ------------------------------------------------------------------ statistics: one thread per position
     const int m = (warp - 8) * 32 + lane;
     bool ok = true;
     for (int i = 0; ok && i < my_tiles; ++i) {
@@ -153,8 +156,8 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       ok = mbar_wait(bars + (Z_FULL + stage) * 8, (i >> 1) & 1, abort_flag);
       if (!ok) break;
       const uint32_t z0 = base + kSmZ + stage * 32768;
-      // Three passes over the 256-byte row in shared memory (sum, squared deviations, write-back), eight 16-byte
-      // loads in flight at a time: keeps the register footprint small; the reads are conflict-free.
+      // two passes over the 256-byte row in shared memory (mean, then squared deviations), eight 16-byte loads in
+      // flight at a time; the reads are conflict-free and nothing is written back
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 8
       for (int c = 0; c < 16; ++c) {
@@ -178,32 +181,27 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
         }
       }
       const float rstd = rsqrtf(((var4[0] + var4[1]) + (var4[2] + var4[3])) * (1.f / kC) + p.eps);
-      const float nmr = -mu * rstd;
-#pragma unroll 8
-      for (int c = 0; c < 16; ++c) {
-        const uint32_t addr = z0 + (c >> 3) * 16384 + sw128_offset(m, c & 7);
-        uint4 x = lds128(addr);
-        x.x = pack_bf16x2(fmaf(bf16_lo(x.x), rstd, nmr), fmaf(bf16_hi(x.x), rstd, nmr));
-        x.y = pack_bf16x2(fmaf(bf16_lo(x.y), rstd, nmr), fmaf(bf16_hi(x.y), rstd, nmr));
-        x.z = pack_bf16x2(fmaf(bf16_lo(x.z), rstd, nmr), fmaf(bf16_hi(x.z), rstd, nmr));
-        x.w = pack_bf16x2(fmaf(bf16_lo(x.w), rstd, nmr), fmaf(bf16_hi(x.w), rstd, nmr));
-        sts128(addr, x);
-      }
-      // The mask values have their own four slots: the epilogue of a tile runs while its z stage is already being
-      // reloaded.  A slot is rewritten three tiles later, when that epilogue is long done (the MMAs of tile t + 1
-      // wait for the accumulators of tile t, and this write for tile t + 3 waits for the MMAs of tile t + 1).
-      reinterpret_cast<float*>(gen + kSmMask + (i & 3) * 512)[m] = mval;
-      fence_proxy_async_smem();  // the MMA reads the tile through the async proxy
+      // Statistics and mask go to one of four slots: the epilogue of a tile reads its slot while the statistics of
+      // the next two tiles are written.  A slot is rewritten four tiles later, when that epilogue is long done
+      // (the MMAs of tile t + 1 wait for the accumulators of tile t, the loads of tile t + 3 for those MMAs).
+      float* slot = reinterpret_cast<float*>(gen + kSmStats + (i & 3) * kStatsSlot);
+      slot[m] = rstd;
+      slot[128 + m] = -mu * rstd;
+      slot[256 + m] = 0.5f * mval;  // sigmoid(g) * v * mask = tanh(g/2) * h + h with h = v * mask / 2
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars + (Z_READY + stage) * 8);
+      if (lane == 0) {
+        mbar_arrive(bars + (STATS_READY + (i & 3)) * 8);
+        mbar_arrive(bars + (Z_EMPTY + stage) * 8);  // done reading the tile
+      }
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ epilogue warps: one thread per channel
     const int wg = warp >> 2;
     const int ch = (warp & 3) * 32 + lane;  // channel inside this warpgroup's 128 == TMEM lane
     const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + wg * 256;
-    const float cg = p.sc[wg * 256 + ch].y, cp = p.sc[wg * 256 + 128 + ch].y;
-    const uint64_t cg2 = pack_f32x2(cg, cg), cp2 = pack_f32x2(cp, cp);
+    const float2 kg = p.sc[wg * 256 + ch], kp = p.sc[wg * 256 + 128 + ch];  // {rowsum, const} of the gate / value row
+    const uint64_t cg2 = pack_f32x2(kg.y, kg.y), cp2 = pack_f32x2(kp.y, kp.y);
+    const uint64_t rg2 = pack_f32x2(kg.x, kg.x), rp2 = pack_f32x2(kp.x, kp.x);
     bool ok = true;
     for (int i = 0; ok && i < my_tiles; ++i) {
       const int tile = blockIdx.x + i * gridDim.x;
@@ -211,11 +209,12 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       const int r = br % p.R, b = br / p.R;
       const int stage = i & 1;
       const float bscale = (wg == 1 && p.b_scale) ? __ldg(p.b_scale + b) : 1.f;
-      const uint64_t hs2 = pack_f32x2(0.5f * bscale, 0.5f * bscale);
-      const float4* mk = reinterpret_cast<const float4*>(gen + kSmMask + (i & 3) * 512);
+      const uint64_t hs2 = pack_f32x2(bscale, bscale);
+      const float4* stats = reinterpret_cast<const float4*>(gen + kSmStats + (i & 3) * kStatsSlot);
       __nv_bfloat16* dst = p.ab + ((long long)(b * 2 + wg) * kTriHidden + ch) * p.R * p.pitch + (long long)r * p.pitch +
                            st * kTileM;
-      ok = mbar_wait(bars + (ACC_FULL + wg) * 8, i & 1, abort_flag);
+      ok = mbar_wait(bars + (STATS_READY + (i & 3)) * 8, (i >> 2) & 1, abort_flag) &&
+           mbar_wait(bars + (ACC_FULL + wg) * 8, i & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
@@ -228,11 +227,13 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
 #pragma unroll
         for (int part = 0; part < 4; ++part) {
           const int pos0 = half * 64 + part * 16;
-          // per position: half of mask (* b scale); sigmoid(g) * v * m = (tanh(g/2) * h + h) with h = v * m / 2
-          uint64_t mh2[8];
+          // per position: rstd, -mean*rstd, mask/2 (* b scale)
+          uint64_t rs2[8], nm2[8], mh2[8];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float4 t = mk[(pos0 >> 2) + j];
+            const float4 a = stats[(pos0 >> 2) + j], n = stats[32 + (pos0 >> 2) + j], t = stats[64 + (pos0 >> 2) + j];
+            rs2[2 * j] = pack_f32x2(a.x, a.y), rs2[2 * j + 1] = pack_f32x2(a.z, a.w);
+            nm2[2 * j] = pack_f32x2(n.x, n.y), nm2[2 * j + 1] = pack_f32x2(n.z, n.w);
             mh2[2 * j] = mul_f32x2(pack_f32x2(t.x, t.y), hs2);
             mh2[2 * j + 1] = mul_f32x2(pack_f32x2(t.z, t.w), hs2);
           }
@@ -246,11 +247,13 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
           uint32_t packed[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            // packed fp32x2 math on two positions; gate rows are pre-halved
+            // packed fp32x2 math on two positions: LayerNorm finished per position, gate rows are pre-halved
             float a0, a1;
-            unpack_f32x2(add_f32x2(pack_f32x2(__uint_as_float(gg[2 * j]), __uint_as_float(gg[2 * j + 1])), cg2), a0, a1);
-            const uint64_t h2 = mul_f32x2(add_f32x2(pack_f32x2(__uint_as_float(vv[2 * j]), __uint_as_float(vv[2 * j + 1])), cp2),
-                                          mh2[j]);
+            unpack_f32x2(fma_f32x2(rs2[j], pack_f32x2(__uint_as_float(gg[2 * j]), __uint_as_float(gg[2 * j + 1])),
+                                   fma_f32x2(nm2[j], rg2, cg2)), a0, a1);
+            const uint64_t val2 = fma_f32x2(rs2[j], pack_f32x2(__uint_as_float(vv[2 * j]), __uint_as_float(vv[2 * j + 1])),
+                                            fma_f32x2(nm2[j], rp2, cp2));
+            const uint64_t h2 = mul_f32x2(val2, mh2[j]);
             float o0, o1;
             unpack_f32x2(fma_f32x2(pack_f32x2(tanh_approx(a0), tanh_approx(a1)), h2, h2), o0, o1);
             packed[j] = pack_bf16x2(o0, o1);
