@@ -14,15 +14,16 @@
 // MMAs run on the raw tile as soon as it has landed, four statistics warps (one thread per position) compute mean
 // and rstd of every position meanwhile, and the epilogue applies rstd[pos]·(D − mean[pos]·rowsum[ch]) + const[ch].
 //
-// Warp roles (448 threads): warps 0-3 epilogue of the a channels, 4-7 of the b channels, 8-11 statistics,
-// warp 12 TMA producer, warp 13 MMA issuer / TMEM owner.
+// Warp roles (704 threads): warps 0-15 epilogue - warpgroup g finishes the a (g < 2) or b (g >= 2) channels for
+// the first (g even) or second (g odd) 64 positions of the tile -, warps 16-19 statistics, warp 20 TMA producer,
+// warp 21 MMA issuer / TMEM owner.
 #include "common.cuh"
 #include "layout.h"
 
 namespace b200ta {
 namespace {
 
-constexpr int kThreads = 448;
+constexpr int kThreads = 704;
 constexpr int kTileM = 128;                 // positions per tile
 constexpr int kSmW = 0;                     // folded rows: 2 halves (64 channels of K each) x 512 rows x 128 B
 constexpr int kWHalf = kTriInRows * 128;    // 64 KiB
@@ -71,21 +72,21 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       mbar_init(bars + (Z_FULL + i) * 8, 1);
       mbar_init(bars + (Z_EMPTY + i) * 8, 5);   // the MMA commit + the four statistics warps have read the tile
       mbar_init(bars + (ACC_FULL + i) * 8, 1);  // per warpgroup
-      mbar_init(bars + (ACC_EMPTY + i) * 8, 4);
+      mbar_init(bars + (ACC_EMPTY + i) * 8, 8);  // two warpgroups read each accumulator pair
     }
     // statistics of a tile written (the four statistics warps): one barrier per statistics slot, because the
     // statistics of tile t + 2 may be complete before the epilogue of tile t has looked at its barrier
     for (int i = 0; i < 4; ++i) mbar_init(bars + (STATS_READY + i) * 8, 4);
     fence_mbar_init();
   }
-  if (warp == 13) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+  if (warp == 21) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int my_tiles = (p.num_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1;
 
-  if (warp == 12) {
+  if (warp == 20) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tm_z);
@@ -112,7 +113,7 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
         mbar_wait(bars + (Z_FULL + (last & 1)) * 8, (last >> 1) & 1, abort_flag + 1);
       }
     }
-  } else if (warp == 13) {
+  } else if (warp == 21) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(128, kTileM);
@@ -141,9 +142,9 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
         umma_commit(bars + (Z_EMPTY + stage) * 8);
       }
     }
-  } else if (warp >= 8 && warp < 12) {
+  } else if (warp >= 16 && warp < 20) {
     // ------------------------------------------------------------------ statistics: one thread per position
-    const int m = (warp - 8) * 32 + lane;
+    const int m = (warp - 16) * 32 + lane;
     bool ok = true;
     for (int i = 0; ok && i < my_tiles; ++i) {
       const int tile = blockIdx.x + i * gridDim.x;
@@ -194,11 +195,13 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
         mbar_arrive(bars + (Z_EMPTY + stage) * 8);  // done reading the tile
       }
     }
-  } else if (warp < 8) {
+  } else if (warp < 16) {
     // ------------------------------------------------------------------ epilogue warps: one thread per channel
-    const int wg = warp >> 2;
-    const int ch = (warp & 3) * 32 + lane;  // channel inside this warpgroup's 128 == TMEM lane
-    const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16) + wg * 256;
+    const int wg = warp >> 3;        // 0: a channels, 1: b channels
+    const int half = (warp >> 2) & 1;  // which 64 positions of the tile
+    const int ch = (warp & 3) * 32 + lane;  // channel inside the 128 == TMEM lane
+    // gate columns of these 64 positions; the value columns lie 128 further
+    const uint32_t acc = tmem_base + (uint32_t((warp & 3) * 32) << 16) + wg * 256 + half * 64;
     const float2 kg = p.sc[wg * 256 + ch], kp = p.sc[wg * 256 + 128 + ch];  // {rowsum, const} of the gate / value row
     const uint64_t cg2 = pack_f32x2(kg.y, kg.y), cp2 = pack_f32x2(kp.y, kp.y);
     const uint64_t rg2 = pack_f32x2(kg.x, kg.x), rp2 = pack_f32x2(kp.x, kp.x);
@@ -207,71 +210,58 @@ trimul_project_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_con
       const int tile = blockIdx.x + i * gridDim.x;
       const int st = tile % p.tiles_s, br = tile / p.tiles_s;
       const int r = br % p.R, b = br / p.R;
-      const int stage = i & 1;
       const float bscale = (wg == 1 && p.b_scale) ? __ldg(p.b_scale + b) : 1.f;
       const uint64_t hs2 = pack_f32x2(bscale, bscale);
-      const float4* stats = reinterpret_cast<const float4*>(gen + kSmStats + (i & 3) * kStatsSlot);
+      // per position: rstd, -mean*rstd, mask/2, as pairs of neighbouring positions
+      const float2* stats = reinterpret_cast<const float2*>(gen + kSmStats + (i & 3) * kStatsSlot) + half * 32;
       __nv_bfloat16* dst = p.ab + ((long long)(b * 2 + wg) * kTriHidden + ch) * p.R * p.pitch + (long long)r * p.pitch +
-                           st * kTileM;
+                           st * kTileM + half * 64;
       ok = mbar_wait(bars + (STATS_READY + (i & 3)) * 8, (i >> 2) & 1, abort_flag) &&
            mbar_wait(bars + (ACC_FULL + wg) * 8, i & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
+      // 8 positions at a time; the TMEM loads of the next chunk are in flight while this one is computed
+      uint32_t g[2][8], v[2][8];
+      tmem_ld8(acc, g[0]);
+      tmem_ld8(acc + 128, v[0]);
+      uint32_t packed[8];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const uint32_t acc = lane_taddr + half * 64;  // gate columns of these 64 positions; the value columns lie 128 further
-        // 16 positions at a time; the TMEM loads of the next chunk are in flight while this one is computed
-        uint32_t g[2][16], v[2][16];
-        tmem_ld16(acc, g[0]);
-        tmem_ld16(acc + 128, v[0]);
-#pragma unroll
-        for (int part = 0; part < 4; ++part) {
-          const int pos0 = half * 64 + part * 16;
-          // per position: rstd, -mean*rstd, mask/2 (* b scale)
-          uint64_t rs2[8], nm2[8], mh2[8];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float4 a = stats[(pos0 >> 2) + j], n = stats[32 + (pos0 >> 2) + j], t = stats[64 + (pos0 >> 2) + j];
-            rs2[2 * j] = pack_f32x2(a.x, a.y), rs2[2 * j + 1] = pack_f32x2(a.z, a.w);
-            nm2[2 * j] = pack_f32x2(n.x, n.y), nm2[2 * j + 1] = pack_f32x2(n.z, n.w);
-            mh2[2 * j] = mul_f32x2(pack_f32x2(t.x, t.y), hs2);
-            mh2[2 * j + 1] = mul_f32x2(pack_f32x2(t.z, t.w), hs2);
-          }
-          tmem_ld_wait();
-          if (part + 1 < 4) {
-            tmem_ld16(acc + (part + 1) * 16, g[(part + 1) & 1]);
-            tmem_ld16(acc + 128 + (part + 1) * 16, v[(part + 1) & 1]);
-          }
-          const uint32_t (&gg)[16] = g[part & 1];
-          const uint32_t (&vv)[16] = v[part & 1];
-          uint32_t packed[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            // packed fp32x2 math on two positions: LayerNorm finished per position, gate rows are pre-halved
-            float a0, a1;
-            unpack_f32x2(fma_f32x2(rs2[j], pack_f32x2(__uint_as_float(gg[2 * j]), __uint_as_float(gg[2 * j + 1])),
-                                   fma_f32x2(nm2[j], rg2, cg2)), a0, a1);
-            const uint64_t val2 = fma_f32x2(rs2[j], pack_f32x2(__uint_as_float(vv[2 * j]), __uint_as_float(vv[2 * j + 1])),
-                                            fma_f32x2(nm2[j], rp2, cp2));
-            const uint64_t h2 = mul_f32x2(val2, mh2[j]);
-            float o0, o1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(tanh_approx(a0), tanh_approx(a1)), h2, h2), o0, o1);
-            packed[j] = pack_bf16x2(o0, o1);
-          }
-          if (st * kTileM + pos0 + 16 <= p.pitch) stg256(dst + pos0, packed);
+      for (int part = 0; part < 8; ++part) {
+        tmem_ld_wait();
+        if (part + 1 < 8) {
+          tmem_ld8(acc + (part + 1) * 8, g[(part + 1) & 1]);
+          tmem_ld8(acc + 128 + (part + 1) * 8, v[(part + 1) & 1]);
         }
+        const uint32_t (&gg)[8] = g[part & 1];
+        const uint32_t (&vv)[8] = v[part & 1];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // packed fp32x2 math on two positions: LayerNorm finished per position, gate rows are pre-halved
+          const float2 rs = stats[part * 4 + j], nm = stats[64 + part * 4 + j], mh = stats[128 + part * 4 + j];
+          const uint64_t rs2 = pack_f32x2(rs.x, rs.y), nm2 = pack_f32x2(nm.x, nm.y);
+          float a0, a1;
+          unpack_f32x2(fma_f32x2(rs2, pack_f32x2(__uint_as_float(gg[2 * j]), __uint_as_float(gg[2 * j + 1])),
+                                 fma_f32x2(nm2, rg2, cg2)), a0, a1);
+          const uint64_t val2 = fma_f32x2(rs2, pack_f32x2(__uint_as_float(vv[2 * j]), __uint_as_float(vv[2 * j + 1])),
+                                          fma_f32x2(nm2, rp2, cp2));
+          // sigmoid(g) * v * mask = tanh(g/2) * h + h with h = v * mask / 2
+          const uint64_t h2 = mul_f32x2(val2, mul_f32x2(pack_f32x2(mh.x, mh.y), hs2));
+          float o0, o1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(tanh_approx(a0), tanh_approx(a1)), h2, h2), o0, o1);
+          packed[(part & 1) * 4 + j] = pack_bf16x2(o0, o1);
+        }
+        if ((part & 1) && st * kTileM + half * 64 + (part - 1) * 8 + 16 <= p.pitch) stg256(dst + (part - 1) * 8, packed);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + (ACC_EMPTY + wg) * 8);
-      if (!ok) break;
     }
   }
 
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (warp == 13) {
+  if (warp == 21) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
