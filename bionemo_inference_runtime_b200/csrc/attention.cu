@@ -322,9 +322,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tc_fence_after();
           const uint32_t d = d0 + w * 128;
           const uint64_t dq = dq0 + w * 512;  // Q of half 1 lies 8 KiB further
-          umma_ss(d, dq, dk, idesc_s, 0u);
-          umma_ss(d, dq + 2, dk + 2, idesc_s, 1u);  // second 16 channels: +32 bytes
-          if (!it.uniform) {
+          if (!it.uniform) {  // a row without a valid key has equal logits: the softmax warps need no scores
+            umma_ss(d, dq, dk, idesc_s, 0u);
+            umma_ss(d, dq + 2, dk + 2, idesc_s, 1u);  // second 16 channels: +32 bytes
             const uint64_t db = db0 + w * 2048;  // bias of half 1 lies 32 KiB further
 #pragma unroll
             for (int j = 0; j < 8; ++j) umma_ts(d, ti + j * 8, db + j * 128, idesc_b1, 1u);
@@ -421,6 +421,34 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ok = mbar_wait(bars + (S_FULL + w) * 8, ct & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
+        if (it.uniform) {
+          // No valid key, eager semantics: every logit is the same, so every probability of the tile is 1 (0 past
+          // the last key) and the output becomes the mean of V.  No scores are read, no exponentials taken.
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + (S_FREE + w) * 8);
+          if (kt > 0) {
+            ok = mbar_wait(bars + (O_FULL + w) * 8, (ct - 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          const int rem = it.len - kt * kKTile;  // keys in this tile
+#pragma unroll
+          for (int qtr = 0; qtr < 4; ++qtr) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const int j0 = qtr * 32 + 2 * e;
+              pk[e] = j0 + 1 < rem ? 0x3F803F80u : (j0 < rem ? 0x00003F80u : 0u);  // bf16 pairs of 1.0
+            }
+            tmem_st16(p_addr + qtr * 16, pk);
+          }
+          row_sum += float(rem < kKTile ? rem : kKTile);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + (P_FULL + w) * 8);
+          continue;
+        }
         float s2[128];  // raw scores (bias included) of this row against the tile's 128 keys
         tmem_ld32_f128<0>(s_addr, s2);
         tmem_ld32_f128<32>(s_addr + 32, s2);
@@ -431,11 +459,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + (S_FREE + w) * 8);  // the S buffer can take the next tile's scores
 
-        if (it.uniform) {
-          // no valid key, eager semantics: every logit is the same
-#pragma unroll
-          for (int j = 0; j < 128; ++j) s2[j] = 0.f;
-        }
         const int rem = it.len - kt * kKTile;  // valid keys in this tile
         if (rem < kKTile) {
 #pragma unroll
