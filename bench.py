@@ -392,7 +392,7 @@ def run_ours(args) -> dict:
 
 
 def run_sharded(args) -> dict:
-    """BASELINE config 5: one pair tensor z[1, 4096, 4096, 128] (3900 valid tokens) row-sharded over the ranks,
+    """Benchmark config 5: one pair tensor z[1, 4096, 4096, 128] (3900 valid tokens) row-sharded over the ranks,
     4 pair-track blocks of start node -> all-to-all -> end node -> transition (-> all-to-all back).  The total work
     is fixed (strong scaling); with one rank the same blocks run on the whole tensor without any exchange."""
     import torch.distributed as dist

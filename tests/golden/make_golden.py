@@ -28,7 +28,7 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = Path(os.environ.get("BIOIR_REFERENCE", "/root/reference"))
+REF = Path(os.environ["BIOIR_REFERENCE"]) if "BIOIR_REFERENCE" in os.environ else None
 sys.dont_write_bytecode = True
 
 
@@ -91,13 +91,15 @@ def save(name: str, **arrays) -> None:
 
 
 def main() -> None:
+    if REF is None:
+        raise SystemExit("set BIOIR_REFERENCE to the reference checkout")
     install_shim()
     from bionemo_ir._torch.custom_ops.transition_mlp_w_norm import transition_mlp_w_norm_reference
     from bionemo_ir._torch.layers.transition import Transition
     from bionemo_ir._torch.layers.triangle_nodes import TriangleAttentionEndingNode, TriangleAttentionStartingNode
 
     torch.manual_seed(0)
-    # ---- case 1: starting node, all-ones mask, gate bias 1, identity LayerNorm (BASELINE config 1, shrunk)
+    # ---- case 1: starting node, all-ones mask, gate bias 1, identity LayerNorm (the reference's CPU benchmark case, shrunk)
     g = torch.Generator().manual_seed(1000)
     N = 24
     z = torch.randn(1, N, N, 128, generator=g).bfloat16().float()

@@ -84,7 +84,7 @@ def test_shape_sweep_with_padding_and_biases(n, direction):
 
 
 def test_config4_token_count_and_unmasked_call():
-    """N = 768 (the pair track of BASELINE config 4), no mask; sampled against the oracle on the GPU."""
+    """N = 768 (the token count of the 48-block trunk benchmark), no mask; checked against the oracle on the GPU."""
     torch.manual_seed(4)
     n = 768
     w = bf16(orc.make_trimul_weights(44))
