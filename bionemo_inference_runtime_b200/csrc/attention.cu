@@ -5,7 +5,7 @@
 // where `bias` is the triangle bias already divided by `scale` and `gate` holds sigmoid(gate logits) (the
 // prologue writes both that way).
 // The N x N x N logits never exist in memory: a CTA owns 256 queries of one (b, r, h), walks the
-// keys in tiles of 128 and keeps a running max / sum per query and the output in TMEM.
+// keys in tiles of 128 and keeps a reference point and a running sum per query and the output in TMEM.
 //
 // Everything that touches a score matrix element is either a tensor-core or a TMEM operation:
 //   TMA      K tile, V tile and the two 128x128 bias tiles (one per 128-query half) -> shared memory
@@ -21,9 +21,12 @@
 // tensor core.  The MMA warp runs one key tile ahead (also across work items), so the next scores are
 // in TMEM before a warpgroup asks for them.
 //
+// A pair row without a valid key takes a constant path in "uniform" mode (probabilities all 1: the output is the
+// mean of V, as the eager reference computes it) and is skipped in "zeros" mode.
+//
 // Warp roles (384 threads): warps 0-3 softmax half 0, warps 4-7 softmax half 1, warp 8 TMA producer,
-// warp 9 score-MMA issuer / TMEM owner, warp 10 P·V-MMA issuer, warp 11 idle.  The third warpgroup gives most of its registers to
-// the softmax warpgroups (setmaxnreg).
+// warp 9 score-MMA issuer / TMEM owner, warp 10 P·V-MMA issuer, warp 11 idle.  The third warpgroup gives most
+// of its registers to the softmax warpgroups (setmaxnreg).
 #include "common.cuh"
 #include "layout.h"
 

@@ -4,11 +4,11 @@
 // activation block arrives by TMA as the K-major A operand, the weights (resident in shared memory for the
 // whole kernel) are the B operand, tcgen05.mma accumulates into TMEM and eight epilogue warps (one TMEM lane =
 // one position = one thread per warpgroup, the two warpgroups take alternate 32-column groups) finish the rows
-// and store them with 16-byte vector stores (64 contiguous bytes per thread and group).
+// and store them with 32-byte vector stores where alignment allows (64 contiguous bytes per thread and group).
 //
 //   kPrologue: z tile -> LayerNorm statistics (from the smem copy) while the tensor core multiplies the raw
-//              rows with the LayerNorm-folded weights: q,k,v,g (512 columns, written head-major) and 4
-//              triangle-bias heads.
+//              rows with the LayerNorm-folded weights: q,k,v,g (512 columns, written head-major; the g plane
+//              as sigmoid(g)) and 4 triangle-bias heads.
 //   kEpilogue: og tile -> og · W_oᵀ + b_o + residual.
 //
 // Warp roles (320 threads): warps 0-7 epilogue (TMEM lanes 32(w%4)..+31), warp 8 TMA producer, warp 9 MMA
