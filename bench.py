@@ -424,7 +424,8 @@ def run_sharded(args) -> dict:
                                           orc.make_transition_weights(3002 + 3 * k), device)
         blocks.append((start, end, trans))
     if world > 1:
-        drivers = [sharded.ShardedPairBlock(s, e, t) for s, e, t in blocks]
+        fused = args.exchange == "peer_stores"
+        drivers = [sharded.ShardedPairBlock(s, e, t, fused_transpose=fused) for s, e, t in blocks]
 
         def step(z):
             for d in drivers:
@@ -517,8 +518,11 @@ def run_sharded(args) -> dict:
         "config": {"workload": f"{args.workload}: {cfg['desc']}", "tokens": N, "valid_lengths": cfg["valid"],
                    "blocks": nblocks, "block_ms": ms / nblocks, "l2": "inputs far larger than L2 (4.3 GB pair tensor)",
                    "empty_row_mode": "uniform",
-                   "parallelism": f"pair rows sharded x{world}; per block 2 all-to-all of {a2a_bytes} B per rank and "
-                                  f"2 all-gathers of the triangle bias" if world > 1 else "single GPU, no exchange"},
+                   "parallelism": (f"pair rows sharded x{world}; per block "
+                                   + ("1 transpose by peer stores from the output kernel and 1 all-to-all"
+                                      if args.exchange == "peer_stores" else "2 all-to-all")
+                                   + f" of {a2a_bytes} B per rank and 2 all-gathers of the triangle bias")
+                   if world > 1 else "single GPU, no exchange"},
         "e2e": {"value": flops_total / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": shard_bytes, "d2h_bytes_per_step": shard_bytes},
         "gpu_launches": launches * args.steps,
@@ -614,6 +618,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
+    ap.add_argument("--exchange", choices=["all_to_all", "peer_stores"], default="all_to_all",
+                    help="sharded workloads: how the rows->columns transpose crosses the links (NCCL all-to-all, or "
+                         "stores from the starting node's output kernel into the peers' column shards)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.steps is None:

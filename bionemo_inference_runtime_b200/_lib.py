@@ -68,6 +68,11 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p],
     ),
+    "b200ta_epilogue_scatter": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int, c_int,
+         c_int, c_int, c_int, c_void_p],
+    ),
     "b200ta_trimul_pack_bytes": (c_size_t, []),
     "b200ta_pack_trimul_weights": (c_int, [c_void_p] * 12 + [c_int, c_void_p, c_void_p]),
     "b200ta_trimul_project": (

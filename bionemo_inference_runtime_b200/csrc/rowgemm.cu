@@ -24,6 +24,7 @@ constexpr int kThreads = 320;
 constexpr int kSlotCols = 256;  // TMEM columns per accumulator slot (2 slots)
 
 enum Mode { kPrologue = 0, kEpilogue = 1 };
+constexpr int kMaxPeers = 8;
 
 struct RowGemmParams {
   int B, R, S, S_pad;
@@ -38,6 +39,10 @@ struct RowGemmParams {
   __nv_bfloat16* out;                         // prologue: q/k/v/g planes; epilogue: output pair tensor
   long long qs_which, qs_br, qs_h, qs_s;      // prologue strides (elements)
   long long os_b, os_r, os_s;                 // epilogue strides (elements)
+  // epilogue, transposing mode (num_peers > 0): position (b, r, s) goes to the column shard of GPU s / peer_cols,
+  // a [B][peer_rows][peer_cols][128] tensor, at (b, row0 + r, s % peer_cols)
+  __nv_bfloat16* peers[kMaxPeers];
+  int num_peers, peer_cols, peer_rows, row0;
   int want_qkvg;
   int has_residual;
   int wide_store;  // output base 32-byte aligned and every stride a multiple of 16 elements
@@ -339,7 +344,14 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 packed[j] = pack_bf16x2(o0, o1);
               }
               if (s < p.S) {
-                __nv_bfloat16* dst = p.out + b * p.os_b + r * p.os_r + (long long)s * p.os_s + n0;
+                __nv_bfloat16* dst;
+                if (p.num_peers > 0) {
+                  const int peer = s / p.peer_cols;
+                  dst = p.peers[peer] +
+                        (((long long)b * p.peer_rows + p.row0 + r) * p.peer_cols + (s - peer * p.peer_cols)) * kC + n0;
+                } else {
+                  dst = p.out + b * p.os_b + r * p.os_r + (long long)s * p.os_s + n0;
+                }
                 store_row64(dst, packed, p.wide_store != 0);
               }
             }
@@ -381,6 +393,52 @@ int pair_tensor_map(CUtensorMap* map, const void* ptr, int64_t sb, int64_t sr, i
   uint64_t strides[3] = {fix(ss, S), fix(sr, R), fix(sb, B)};
   uint32_t box[4] = {box_c, box_s, 1, 1};
   return encode_tensor_map(map, ptr, 2, 4, dims, strides, box, swz, what);
+}
+
+// Shared by the two epilogue entry points: `p` arrives with its output addressing filled in.
+int launch_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, const void* packed, const void* residual,
+                    int64_t rs_b, int64_t rs_r, int64_t rs_s, RowGemmParams p, int B, int R, int S, void* stream) {
+  B200TA_REQUIRE(og && packed, "epilogue: NULL pointer");
+  B200TA_REQUIRE(B > 0 && R > 0 && S > 0, "epilogue: bad sizes B=%d R=%d S=%d", B, R, S);
+  B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "epilogue: packed must be 256-byte aligned");
+  int rc = check_strides("epilogue og", gs_b, gs_r, gs_s);
+  if (rc == B200TA_OK && residual) rc = check_strides("epilogue residual", rs_b, rs_r, rs_s);
+  if (rc != B200TA_OK) return rc;
+  DeviceState* st = nullptr;
+  rc = get_device_state(&st);
+  if (rc != B200TA_OK) return rc;
+
+  CUtensorMap tm_a, tm_w, tm_res;
+  rc = pair_tensor_map(&tm_a, og, gs_b, gs_r, gs_s, B, R, S, 64, kTileM, SWZ_128, "epilogue og");
+  if (rc != B200TA_OK) return rc;
+  const char* pk = static_cast<const char*>(packed);
+  {
+    uint64_t dims[2] = {uint64_t(kC), uint64_t(kC)};
+    uint64_t strides[1] = {uint64_t(kC) * 2};
+    uint32_t box[2] = {64, 128};
+    rc = encode_tensor_map(&tm_w, pk + kNodeWoOff, 2, 2, dims, strides, box, SWZ_128, "epilogue weights");
+    if (rc != B200TA_OK) return rc;
+  }
+  if (residual) {
+    rc = pair_tensor_map(&tm_res, residual, rs_b, rs_r, rs_s, B, R, S, 32, kTileM, SWZ_64, "epilogue residual");
+    if (rc != B200TA_OK) return rc;
+  } else {
+    tm_res = tm_a;
+  }
+  p.B = B, p.R = R, p.S = S, p.S_pad = S;
+  p.tiles_s = (S + kTileM - 1) / kTileM;
+  p.num_tiles = B * R * p.tiles_s;
+  p.bo = reinterpret_cast<const float*>(pk + kNodeBoOff);
+  p.flags = reinterpret_cast<const int*>(pk + kNodeFlagsOff);
+  p.has_residual = residual ? 1 : 0;
+  p.status = st->status_dev;
+
+  auto kern = rowgemm_kernel<kEpilogue>;
+  B200TA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<kEpilogue>::kDynamic));
+  const int grid = p.num_tiles < st->num_sms ? p.num_tiles : st->num_sms;
+  kern<<<grid, kThreads, Smem<kEpilogue>::kDynamic, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_w, tm_res, p);
+  B200TA_CHECK_CUDA(cudaGetLastError());
+  return B200TA_OK;
 }
 
 }  // namespace
@@ -450,54 +508,35 @@ int b200ta_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, co
                     const void* residual, int64_t rs_b, int64_t rs_r, int64_t rs_s, void* out, int64_t os_b,
                     int64_t os_r, int64_t os_s, int B, int R, int S, void* stream) {
   using namespace b200ta;
-  B200TA_REQUIRE(og && packed && out, "epilogue: NULL pointer");
-  B200TA_REQUIRE(B > 0 && R > 0 && S > 0, "epilogue: bad sizes B=%d R=%d S=%d", B, R, S);
-  B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "epilogue: packed must be 256-byte aligned");
+  B200TA_REQUIRE(out, "epilogue: NULL pointer");
   B200TA_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15u) == 0, "epilogue: out must be 16-byte aligned");
-  int rc = check_strides("epilogue og", gs_b, gs_r, gs_s);
-  if (rc == B200TA_OK) rc = check_strides("epilogue out", os_b, os_r, os_s);
-  if (rc == B200TA_OK && residual) rc = check_strides("epilogue residual", rs_b, rs_r, rs_s);
+  int rc = check_strides("epilogue out", os_b, os_r, os_s);
   if (rc != B200TA_OK) return rc;
-  DeviceState* st = nullptr;
-  rc = get_device_state(&st);
-  if (rc != B200TA_OK) return rc;
-
-  CUtensorMap tm_a, tm_w, tm_res;
-  rc = pair_tensor_map(&tm_a, og, gs_b, gs_r, gs_s, B, R, S, 64, kTileM, SWZ_128, "epilogue og");
-  if (rc != B200TA_OK) return rc;
-  const char* pk = static_cast<const char*>(packed);
-  {
-    uint64_t dims[2] = {uint64_t(kC), uint64_t(kC)};
-    uint64_t strides[1] = {uint64_t(kC) * 2};
-    uint32_t box[2] = {64, 128};
-    rc = encode_tensor_map(&tm_w, pk + kNodeWoOff, 2, 2, dims, strides, box, SWZ_128, "epilogue weights");
-    if (rc != B200TA_OK) return rc;
-  }
-  if (residual) {
-    rc = pair_tensor_map(&tm_res, residual, rs_b, rs_r, rs_s, B, R, S, 32, kTileM, SWZ_64, "epilogue residual");
-    if (rc != B200TA_OK) return rc;
-  } else {
-    tm_res = tm_a;
-  }
-
   RowGemmParams p{};
-  p.B = B, p.R = R, p.S = S, p.S_pad = S;
-  p.tiles_s = (S + kTileM - 1) / kTileM;
-  p.num_tiles = B * R * p.tiles_s;
-  p.bo = reinterpret_cast<const float*>(pk + kNodeBoOff);
-  p.flags = reinterpret_cast<const int*>(pk + kNodeFlagsOff);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.os_b = os_b, p.os_r = os_r, p.os_s = os_s;
-  p.has_residual = residual ? 1 : 0;
   p.wide_store = (reinterpret_cast<uintptr_t>(out) & 31u) == 0 && os_b % 16 == 0 && os_r % 16 == 0 && os_s % 16 == 0;
-  p.status = st->status_dev;
+  return launch_epilogue(og, gs_b, gs_r, gs_s, packed, residual, rs_b, rs_r, rs_s, p, B, R, S, stream);
+}
 
-  auto kern = rowgemm_kernel<kEpilogue>;
-  B200TA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<kEpilogue>::kDynamic));
-  const int grid = p.num_tiles < st->num_sms ? p.num_tiles : st->num_sms;
-  kern<<<grid, kThreads, Smem<kEpilogue>::kDynamic, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_w, tm_res, p);
-  B200TA_CHECK_CUDA(cudaGetLastError());
-  return B200TA_OK;
+int b200ta_epilogue_scatter(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, const void* packed,
+                            const void* residual, int64_t rs_b, int64_t rs_r, int64_t rs_s, void* const* peer_out,
+                            int num_peers, int rank, int B, int R, int S, void* stream) {
+  using namespace b200ta;
+  B200TA_REQUIRE(peer_out, "epilogue_scatter: NULL pointer");
+  B200TA_REQUIRE(num_peers >= 1 && num_peers <= kMaxPeers && rank >= 0 && rank < num_peers,
+                 "epilogue_scatter: need 1..%d peers and 0 <= rank < peers, got %d and %d", kMaxPeers, num_peers, rank);
+  B200TA_REQUIRE(S % num_peers == 0 && R == S / num_peers,
+                 "epilogue_scatter: S=%d must be divisible by the %d peers and R=%d must equal S / peers", S, num_peers, R);
+  RowGemmParams p{};
+  for (int g = 0; g < num_peers; ++g) {
+    B200TA_REQUIRE(peer_out[g] && (reinterpret_cast<uintptr_t>(peer_out[g]) & 31u) == 0,
+                   "epilogue_scatter: peer buffer %d must be a 32-byte aligned device pointer", g);
+    p.peers[g] = static_cast<__nv_bfloat16*>(peer_out[g]);
+  }
+  p.num_peers = num_peers, p.peer_cols = R, p.peer_rows = S, p.row0 = rank * R;
+  p.wide_store = 1;
+  return launch_epilogue(og, gs_b, gs_r, gs_s, packed, residual, rs_b, rs_r, rs_s, p, B, R, S, stream);
 }
 
 }  // extern "C"

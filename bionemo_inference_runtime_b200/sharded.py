@@ -20,11 +20,17 @@ Per block:
 4. transition on the COLS shard (position-wise, layout does not matter).
 5. all-to-all COLS -> ROWS for the next block (``keep_layout=True`` skips it for a caller that continues in COLS).
 
+With ``fused_transpose`` (NCCL groups, CUDA tensors) step 2 is not a collective at all: the starting node's output
+kernel (o_proj + residual) stores every result row straight into the column shard of the GPU that owns it, through
+peer mappings of a symmetric-memory buffer (NVLink stores from inside the kernel), followed by one barrier.  The way back (step 5) stays an NCCL all-to-all.
+
 The compute stages are looked up on a small ``stages`` object so that the orchestration (what is gathered, what
 is exchanged, which strides are used) can be exercised with CPU tensors and the ``gloo`` backend.
 """
 
 from __future__ import annotations
+
+import ctypes
 
 import torch
 import torch.distributed as dist
@@ -59,6 +65,28 @@ class KernelStages:
 
     def transition(self, layer, x: torch.Tensor) -> torch.Tensor:
         return layer(x, residual=True, inplace=True)
+
+    def epilogue_scatter(self, node, og, residual_kernel_order, peer_ptrs: list[int], rank: int):
+        """o_proj + residual of the ROWS shard, written transposed into every GPU's COLS shard (peer stores)."""
+        B, R, S, _ = og.shape
+        packed = node._packed(og.device)
+        r = residual_kernel_order
+        ptrs = (ctypes.c_void_p * len(peer_ptrs))(*peer_ptrs)
+        _lib.call("b200ta_epilogue_scatter", og.data_ptr(), og.stride(0), og.stride(1), og.stride(2), packed.data_ptr(),
+                  r.data_ptr(), *r.stride()[:3], ptrs, len(peer_ptrs), rank, B, R, S,
+                  torch.cuda.current_stream().cuda_stream)
+
+
+class _PeerColumnShard:
+    """The COLS shard ``[B, N, n, c]`` of this rank in symmetric memory, with every rank's mapping of it."""
+
+    def __init__(self, shape, device, group):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.tensor = symm_mem.empty(shape, dtype=torch.bfloat16, device=device)
+        handle = symm_mem.rendezvous(self.tensor, group if group is not None else dist.group.WORLD)
+        self.ptrs = [int(p) for p in handle.buffer_ptrs]
+        self.shape = tuple(shape)
 
 
 def shard(z: torch.Tensor, rank: int, world: int, layout: str = ROWS) -> torch.Tensor:
@@ -108,12 +136,35 @@ def gather_bias(bias_local: torch.Tensor, group=None) -> torch.Tensor:
 class ShardedPairBlock:
     """start node -> exchange -> end node -> transition (-> exchange back) on a sharded pair tensor."""
 
-    def __init__(self, start_node, end_node, transition=None, group=None, stages=None):
+    def __init__(self, start_node, end_node, transition=None, group=None, stages=None, fused_transpose: bool = False):
         self.start_node = start_node
         self.end_node = end_node
         self.transition = transition
         self.group = group
         self.stages = stages if stages is not None else KernelStages()
+        self.fused_transpose = fused_transpose
+        self._cols: _PeerColumnShard | None = None
+
+    def _barrier(self, device) -> None:
+        """Orders the peer stores against the other ranks' reads: a one-element all-reduce on the current stream."""
+        flag = torch.zeros(1, dtype=torch.int32, device=device)
+        dist.all_reduce(flag, group=self.group)
+
+    def _start_node_into_column_shards(self, z_rows: torch.Tensor, lengths_rows) -> torch.Tensor:
+        """The starting node on the ROWS shard with its output written directly into every rank's COLS shard."""
+        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        B, n, N, c = z_rows.shape
+        if self._cols is None or self._cols.shape != (B, N, n, c):
+            self._cols = _PeerColumnShard((B, N, n, c), z_rows.device, self.group)
+        node = self.start_node
+        qkvg, bias_local = self.stages.prologue(node, z_rows)
+        bias_full = gather_bias(bias_local, self.group)
+        og = self.stages.attention(node, qkvg, bias_full, lengths_rows, B, n, N)
+        # The bias all-gather above already orders this call after every rank's last read of its column shard (the
+        # exchange back to rows, or the caller's use of a ``keep_layout`` result, precedes its next call).
+        self.stages.epilogue_scatter(node, og, z_rows, self._cols.ptrs, rank)
+        self._barrier(z_rows.device)  # every rank's stores into this rank's column shard have landed
+        return self._cols.tensor
 
     def _node(self, node, x_shard: torch.Tensor, layout: str, lengths_local: torch.Tensor | None) -> torch.Tensor:
         """One node on the shard whose independent rows are local: ROWS for the starting node, COLS for the ending
@@ -130,9 +181,13 @@ class ShardedPairBlock:
                 lengths_cols: torch.Tensor | None = None, keep_layout: bool = False) -> torch.Tensor:
         """``z_rows``: ROWS shard ``[B, n, N, c]`` (updated in place where possible).  ``lengths_rows[b, i_local]`` =
         valid keys of local pair row i (starting node); ``lengths_cols[b, j_local]`` = valid keys of local pair column
-        j (ending node).  Returns the ROWS shard of the block output (the COLS shard with ``keep_layout``)."""
-        z_rows = self._node(self.start_node, z_rows, ROWS, lengths_rows)
-        z_cols = exchange(z_rows, COLS, self.group)
+        j (ending node).  Returns the ROWS shard of the block output (the COLS shard with ``keep_layout``; with
+        ``fused_transpose`` that is the block's symmetric-memory buffer, valid until the next call)."""
+        if self.fused_transpose:
+            z_cols = self._start_node_into_column_shards(z_rows, lengths_rows)
+        else:
+            z_rows = self._node(self.start_node, z_rows, ROWS, lengths_rows)
+            z_cols = exchange(z_rows, COLS, self.group)
         z_cols = self._node(self.end_node, z_cols, COLS, lengths_cols)
         if self.transition is not None:
             z_cols = self.stages.transition(self.transition, z_cols)

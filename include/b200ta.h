@@ -161,6 +161,20 @@ int b200ta_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, co
                     int64_t os_b, int64_t os_r, int64_t os_s, int B, int R, int S, void* stream);
 
 /*
+ * The same epilogue with its result written transposed into the column shards of the GPUs of one box: the
+ * calling GPU holds the pair rows [rank*R, rank*R + R) of a [B, S, S, 128] pair tensor (R = S / num_peers); the
+ * row (b, rank*R + r) position s goes to GPU s / R, whose column shard is a contiguous [B][S][R][128] bf16
+ * tensor, at (b, rank*R + r, s % R).  peer_out[g] is that shard's address on GPU g as mapped into this process
+ * (peer access over NVLink, e.g. a symmetric-memory allocation); the kernel stores straight into it, so the
+ * all-to-all between the starting and the ending node needs no separate pass.  The caller orders this call
+ * after every GPU has finished reading its shard and orders the readers after it (one barrier on each side).
+ * The reference has no counterpart (its multi-GPU mode is whole-model replicas).
+ */
+int b200ta_epilogue_scatter(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, const void* packed,
+                            const void* residual, int64_t rs_b, int64_t rs_r, int64_t rs_s,
+                            void* const* peer_out, int num_peers, int rank, int B, int R, int S, void* stream);
+
+/*
  * Whole node in one call: prologue -> attention -> epilogue on `stream`, intermediates in `workspace`
  * (b200ta_node_workspace_bytes(B, N) bytes, 256-byte aligned, caller-owned; contents are scratch).
  *

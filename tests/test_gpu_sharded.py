@@ -31,7 +31,7 @@ def _modules(device):
     return node(b200.TriangleAttentionStartingNode, 91), node(b200.TriangleAttentionEndingNode, 92), trans.to(device)
 
 
-def _worker(rank: int, port: int, results):
+def _worker(rank: int, port: int, fused: bool, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     device = torch.device("cuda", rank)
@@ -45,8 +45,10 @@ def _worker(rank: int, port: int, results):
         n = N // WORLD
         idx = torch.arange(rank * n, (rank + 1) * n, device=device)
         lengths = torch.where(idx < VALID, VALID, 0).to(torch.int32).reshape(1, n)
-        block = sharded.ShardedPairBlock(start, end, trans)
+        block = sharded.ShardedPairBlock(start, end, trans, fused_transpose=fused)
         out_rows = block(sharded.shard(z, rank, WORLD), lengths, lengths)
+        if fused:  # a second call reuses the symmetric-memory column shard
+            out_rows = block(sharded.shard(z, rank, WORLD), lengths, lengths)
         gathered = [torch.empty_like(out_rows) for _ in range(WORLD)]
         dist.all_gather(gathered, out_rows)
         torch.cuda.synchronize()
@@ -63,11 +65,12 @@ def _worker(rank: int, port: int, results):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < WORLD, reason="needs 2 GPUs")
-def test_sharded_block_on_two_gpus_equals_single_gpu():
+@pytest.mark.parametrize("fused", [False, True], ids=["all_to_all", "peer_stores"])
+def test_sharded_block_on_two_gpus_equals_single_gpu(fused):
     ctx = mp.get_context("spawn")
     results = ctx.Queue()
     port = 29500 + os.getpid() % 2000
-    procs = [ctx.Process(target=_worker, args=(r, port, results)) for r in range(WORLD)]
+    procs = [ctx.Process(target=_worker, args=(r, port + int(fused), fused, results)) for r in range(WORLD)]
     for p in procs:
         p.start()
     equal, max_diff, status = results.get(timeout=300)
