@@ -618,7 +618,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
-    ap.add_argument("--exchange", choices=["all_to_all", "peer_stores"], default="all_to_all",
+    ap.add_argument("--exchange", choices=["all_to_all", "peer_stores"], default="peer_stores",
                     help="sharded workloads: how the rows->columns transpose crosses the links (NCCL all-to-all, or "
                          "stores from the starting node's output kernel into the peers' column shards)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

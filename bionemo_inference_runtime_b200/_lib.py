@@ -68,6 +68,10 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p],
     ),
+    "b200ta_transition_scatter": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ),
     "b200ta_epilogue_scatter": (
         c_int,
         [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int, c_int,

@@ -33,6 +33,18 @@ struct TransParams {
   float eps;
   int add_residual;
   int* status;
+  // scatter form (num_peers > 0): the input is a column shard [B][tokens][cols][128]; row (b, i, j) is stored to
+  // GPU i / cols at row (b, i % cols, col0 + j) of its row shard [B][cols][tokens][128]
+  int num_peers;
+  int cols;
+  int tokens;
+  int col0;
+};
+
+constexpr int kMaxPeers = 8;
+// One output map per GPU; the plain form uses m[0] only.
+struct OutMaps {
+  CUtensorMap m[kMaxPeers];
 };
 
 // shared memory map
@@ -55,7 +67,7 @@ constexpr uint32_t kTmemAcc1 = 0, kTmemAcc2 = 256, kTmemCols = 512;
 
 __global__ void __launch_bounds__(kThreads, 1)
 transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w1,
-                  const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_out,
+                  const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ OutMaps tm_outs,
                   const TransParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -105,7 +117,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       tma_prefetch_desc(&tm_x);
       tma_prefetch_desc(&tm_w1);
       tma_prefetch_desc(&tm_w2);
-      tma_prefetch_desc(&tm_out);
+      tma_prefetch_desc(&tm_outs.m[0]);
       bool ok = true;
       int c = 0;  // chunk counter
       for (int i = 0; ok && i < my_tiles; ++i) {
@@ -323,7 +335,16 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         __syncwarp();
         if (lane == 0) {
           const long long row0 = (long long)tile * kTileM + (warp & 3) * 32;
-          if (row0 < p.rows) tma_store_2d(&tm_out, slab, e * 64 + g * 32, int(row0));
+          const CUtensorMap* tm = &tm_outs.m[0];
+          long long dst0 = row0;
+          if (p.num_peers > 0) {  // 32 consecutive rows share (b, i): cols is a multiple of 32
+            const long long bi = row0 / p.cols;
+            const int j = int(row0 - bi * p.cols), i = int(bi % p.tokens), b = int(bi / p.tokens);
+            const int peer = i / p.cols;
+            tm = &tm_outs.m[peer];
+            dst0 = ((long long)b * p.cols + (i - peer * p.cols)) * p.tokens + p.col0 + j;
+          }
+          if (row0 < p.rows) tma_store_2d(tm, slab, e * 64 + g * 32, int(dst0));
           tma_store_commit();
         }
       }
@@ -350,12 +371,14 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 }  // namespace
 }  // namespace b200ta
 
-extern "C" {
+namespace b200ta {
+namespace {
 
-int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* packed, float eps, void* out,
-                      int64_t os, int64_t rows, int add_residual, void* stream) {
-  using namespace b200ta;
-  B200TA_REQUIRE(x && packed && out, "transition: NULL pointer");
+// outs[0..num_outs): the output (plain form, one entry, row stride os) or every GPU's row shard (scatter form).
+int launch_transition(const void* x, int64_t xs, const void* mask, const void* packed, float eps, void* const* outs,
+                      int num_outs, int64_t os, int64_t rows, int add_residual, int num_peers, int cols, int tokens,
+                      int col0, void* stream) {
+  B200TA_REQUIRE(x && packed && outs, "transition: NULL pointer");
   B200TA_REQUIRE(rows > 0 && rows < (int64_t(1) << 31), "transition: rows=%lld out of range", (long long)rows);
   B200TA_REQUIRE(xs >= kC && xs % 8 == 0 && os >= kC && os % 8 == 0, "transition: row strides must be >= 128 and multiples of 8 elements");
   B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "transition: packed must be 256-byte aligned");
@@ -364,7 +387,8 @@ int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* p
   if (rc != B200TA_OK) return rc;
   const char* pk = static_cast<const char*>(packed);
 
-  CUtensorMap tm_x, tm_w1, tm_w2, tm_out;
+  CUtensorMap tm_x, tm_w1, tm_w2;
+  OutMaps tm_outs;
   {
     uint64_t dims[2] = {uint64_t(kC), uint64_t(rows)};
     uint64_t strides[1] = {uint64_t(xs) * 2};
@@ -373,8 +397,12 @@ int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* p
     if (rc != B200TA_OK) return rc;
     uint64_t ostrides[1] = {uint64_t(os) * 2};
     uint32_t obox[2] = {32, 32};
-    rc = encode_tensor_map(&tm_out, out, 2, 2, dims, ostrides, obox, SWZ_64, "transition out");
-    if (rc != B200TA_OK) return rc;
+    for (int k = 0; k < kMaxPeers; ++k) {
+      const int src = k < num_outs ? k : 0;
+      B200TA_REQUIRE(outs[src], "transition: NULL output pointer");
+      rc = encode_tensor_map(&tm_outs.m[k], outs[src], 2, 2, dims, ostrides, obox, SWZ_64, "transition out");
+      if (rc != B200TA_OK) return rc;
+    }
   }
   {
     uint64_t dims[2] = {uint64_t(kC), uint64_t(kTransRows)};
@@ -400,12 +428,33 @@ int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* p
   p.eps = eps;
   p.add_residual = add_residual ? 1 : 0;
   p.status = st->status_dev;
+  p.num_peers = num_peers, p.cols = cols, p.tokens = tokens, p.col0 = col0;
 
   B200TA_CHECK_CUDA(cudaFuncSetAttribute(transition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmDynamic));
   const int grid = p.num_tiles < st->num_sms ? p.num_tiles : st->num_sms;
-  transition_kernel<<<grid, kThreads, kSmDynamic, static_cast<cudaStream_t>(stream)>>>(tm_x, tm_w1, tm_w2, tm_out, p);
+  transition_kernel<<<grid, kThreads, kSmDynamic, static_cast<cudaStream_t>(stream)>>>(tm_x, tm_w1, tm_w2, tm_outs, p);
   B200TA_CHECK_CUDA(cudaGetLastError());
   return B200TA_OK;
+}
+
+}  // namespace
+}  // namespace b200ta
+
+extern "C" {
+
+int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* packed, float eps, void* out,
+                      int64_t os, int64_t rows, int add_residual, void* stream) {
+  return b200ta::launch_transition(x, xs, mask, packed, eps, &out, 1, os, rows, add_residual, 0, 0, 0, 0, stream);
+}
+
+int b200ta_transition_scatter(const void* x, const void* mask, const void* packed, float eps, void* const* peer_out,
+                              int num_peers, int rank, int B, int tokens, int cols, int add_residual, void* stream) {
+  B200TA_REQUIRE(peer_out && num_peers >= 1 && num_peers <= b200ta::kMaxPeers && rank >= 0 && rank < num_peers,
+                 "transition_scatter: need 1..%d peers and a rank among them", b200ta::kMaxPeers);
+  B200TA_REQUIRE(B > 0 && cols > 0 && cols % 32 == 0 && tokens == cols * num_peers,
+                 "transition_scatter: tokens=%d must be cols=%d x peers=%d and cols a multiple of 32", tokens, cols, num_peers);
+  return b200ta::launch_transition(x, b200ta::kC, mask, packed, eps, peer_out, num_peers, b200ta::kC,
+                                   int64_t(B) * tokens * cols, add_residual, num_peers, cols, tokens, rank * cols, stream);
 }
 
 }  // extern "C"

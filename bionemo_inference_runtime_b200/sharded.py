@@ -22,7 +22,9 @@ Per block:
 
 With ``fused_transpose`` (NCCL groups, CUDA tensors) step 2 is not a collective at all: the starting node's output
 kernel (o_proj + residual) stores every result row straight into the column shard of the GPU that owns it, through
-peer mappings of a symmetric-memory buffer (NVLink stores from inside the kernel), followed by one barrier.  The way back (step 5) stays an NCCL all-to-all.
+peer mappings of a symmetric-memory buffer (NVLink stores from inside the kernel), followed by one barrier.  The way
+back (step 5) is fused the same way into the transition, whose TMA stores go to the row shard of the owning GPU
+(column counts per GPU that are multiples of 32; otherwise, and without a transition, it stays an all-to-all).
 
 The compute stages are looked up on a small ``stages`` object so that the orchestration (what is gathered, what
 is exchanged, which strides are used) can be exercised with CPU tensors and the ``gloo`` backend.
@@ -77,8 +79,18 @@ class KernelStages:
                   torch.cuda.current_stream().cuda_stream)
 
 
-class _PeerColumnShard:
-    """The COLS shard ``[B, N, n, c]`` of this rank in symmetric memory, with every rank's mapping of it."""
+    def transition_scatter(self, layer, x_cols, peer_ptrs: list[int], rank: int):
+        """The transition (+ residual) of the COLS shard, written into every GPU's ROWS shard (peer TMA stores)."""
+        B, N, n, _ = x_cols.shape
+        ptrs = (ctypes.c_void_p * len(peer_ptrs))(*peer_ptrs)
+        eps = layer.eps if layer.norm is None else layer.norm.eps
+        _lib.call("b200ta_transition_scatter", x_cols.data_ptr(), None, layer._packed(x_cols.device).data_ptr(), eps,
+                  ptrs, len(peer_ptrs), rank, B, N, n, 1, torch.cuda.current_stream().cuda_stream)
+
+
+class _PeerShard:
+    """A shard of this rank (``[B, N, n, c]`` COLS or ``[B, n, N, c]`` ROWS) in symmetric memory, with every rank's
+    mapping of it."""
 
     def __init__(self, shape, device, group):
         import torch.distributed._symmetric_memory as symm_mem
@@ -143,7 +155,8 @@ class ShardedPairBlock:
         self.group = group
         self.stages = stages if stages is not None else KernelStages()
         self.fused_transpose = fused_transpose
-        self._cols: _PeerColumnShard | None = None
+        self._cols: _PeerShard | None = None
+        self._rows: _PeerShard | None = None
 
     def _barrier(self, device) -> None:
         """Orders the peer stores against the other ranks' reads: a one-element all-reduce on the current stream."""
@@ -155,7 +168,7 @@ class ShardedPairBlock:
         world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         B, n, N, c = z_rows.shape
         if self._cols is None or self._cols.shape != (B, N, n, c):
-            self._cols = _PeerColumnShard((B, N, n, c), z_rows.device, self.group)
+            self._cols = _PeerShard((B, N, n, c), z_rows.device, self.group)
         node = self.start_node
         qkvg, bias_local = self.stages.prologue(node, z_rows)
         bias_full = gather_bias(bias_local, self.group)
@@ -181,14 +194,24 @@ class ShardedPairBlock:
                 lengths_cols: torch.Tensor | None = None, keep_layout: bool = False) -> torch.Tensor:
         """``z_rows``: ROWS shard ``[B, n, N, c]`` (updated in place where possible).  ``lengths_rows[b, i_local]`` =
         valid keys of local pair row i (starting node); ``lengths_cols[b, j_local]`` = valid keys of local pair column
-        j (ending node).  Returns the ROWS shard of the block output (the COLS shard with ``keep_layout``; with
-        ``fused_transpose`` that is the block's symmetric-memory buffer, valid until the next call)."""
+        j (ending node).  Returns the ROWS shard of the block output (the COLS shard with ``keep_layout``); with
+        ``fused_transpose`` the result is one of the block's symmetric-memory buffers, valid until the next call
+        (it may be passed back in as the next call's ``z_rows``)."""
         if self.fused_transpose:
             z_cols = self._start_node_into_column_shards(z_rows, lengths_rows)
         else:
             z_rows = self._node(self.start_node, z_rows, ROWS, lengths_rows)
             z_cols = exchange(z_rows, COLS, self.group)
         z_cols = self._node(self.end_node, z_cols, COLS, lengths_cols)
+        B, N, n, c = z_cols.shape
+        if self.fused_transpose and self.transition is not None and not keep_layout and n % 32 == 0:
+            if self._rows is None or self._rows.shape != (B, n, N, c):
+                self._rows = _PeerShard((B, n, N, c), z_cols.device, self.group)
+            # every rank has read its row shard of the previous call (prologue and residual of the starting node)
+            # before the barrier that follows the starting node of this call
+            self.stages.transition_scatter(self.transition, z_cols, self._rows.ptrs, dist.get_rank(self.group))
+            self._barrier(z_cols.device)  # every rank's stores into this rank's row shard have landed
+            return self._rows.tensor
         if self.transition is not None:
             z_cols = self.stages.transition(self.transition, z_cols)
         return z_cols if keep_layout else exchange(z_cols, ROWS, self.group)

@@ -230,6 +230,20 @@ int b200ta_node_forward_static(const void* z, int64_t zs_b, int64_t zs_r, int64_
 int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* packed, float eps,
                       void* out, int64_t os, int64_t rows, int add_residual, void* stream);
 
+/*
+ * The transition of a column shard x = [B][tokens][cols][128] (contiguous bf16, cols = tokens / num_peers, a
+ * multiple of 32; this GPU holds the pair columns [rank*cols, rank*cols + cols)) with its result written into the
+ * row shards of the GPUs of one box: position (b, i, j) goes to GPU i / cols, whose row shard is a contiguous
+ * [B][cols][tokens][128] bf16 tensor, at (b, i % cols, rank*cols + j).  peer_out[g] is that shard's address on
+ * GPU g as mapped into this process; the kernel's TMA stores go straight to it, so the all-to-all that returns a
+ * row-sharded pair tensor to row order needs no separate pass.  mask: one bf16 value per position of x, or NULL.
+ * The caller orders this call after every GPU has finished reading its row shard and orders the readers after it.
+ * The reference has no counterpart (its multi-GPU mode is whole-model replicas).
+ */
+int b200ta_transition_scatter(const void* x, const void* mask, const void* packed, float eps,
+                              void* const* peer_out, int num_peers, int rank, int B, int tokens, int cols,
+                              int add_residual, void* stream);
+
 /* ---- triangle multiplication ---------------------------------------------------------
  *
  * update = sigmoid(LN_in(z)·W_goᵀ) ⊙ ( LN_out(t)·W_poᵀ ),   t[b,i,j,d] = Σ_k a[b,i,k,d]·b[b,j,k,d]  (outgoing)
