@@ -68,6 +68,18 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p],
     ),
+    "b200ta_pack_pair_bias_weights": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p]),
+    "b200ta_pair_bias": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int,
+         c_int, c_int, c_int, c_int, c_void_p],
+    ),
+    "b200ta_row_stats": (c_int, [c_void_p, c_int64, c_int64, c_int, c_float, c_void_p, c_void_p]),
+    "b200ta_linear": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+         c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ),
     "b200ta_transition_scatter": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],

@@ -31,7 +31,7 @@ __global__ void fold_rows_kernel(const void* wa, int rows_a, const void* wb, int
   __shared__ float red[3][4];
   float w = 0.f, b = 0.f;
   if (n < rows_a) {
-    w = load_w(wa, dtype, size_t(n) * kC + c);
+    if (wa != nullptr) w = load_w(wa, dtype, size_t(n) * kC + c);
     if (bias_a != nullptr) b = load_w(bias_a, dtype, n);
   } else if (n < rows_a + rows_b) {
     w = load_w(wb, dtype, size_t(n - rows_a) * kC + c);
@@ -104,6 +104,28 @@ int b200ta_pack_node_weights(const void* ln_w, const void* ln_b, const void* w_i
   convert_kernel<<<(kC * kC + 255) / 256, 256, 0, s>>>(w_out, weight_dtype, size_t(kC) * kC,
                                                        reinterpret_cast<__nv_bfloat16*>(base + kNodeWoOff), nullptr);
   convert_kernel<<<1, kC, 0, s>>>(b_out, weight_dtype, kC, nullptr, reinterpret_cast<float*>(base + kNodeBoOff));
+  B200TA_CHECK_CUDA(cudaGetLastError());
+  return B200TA_OK;
+}
+
+int b200ta_pack_pair_bias_weights(const void* ln_w, const void* ln_b, const void* w_z, int num_heads,
+                                  float bias_scale, int weight_dtype, void* packed, void* stream) {
+  using namespace b200ta;
+  B200TA_REQUIRE(w_z && packed, "pack_pair_bias_weights: NULL pointer");
+  B200TA_REQUIRE(num_heads > 0 && num_heads <= 16, "pack_pair_bias_weights: num_heads=%d must be 1..16", num_heads);
+  B200TA_REQUIRE((ln_w == nullptr) == (ln_b == nullptr), "pack_pair_bias_weights: pass both LayerNorm vectors or neither");
+  B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "pack_pair_bias_weights: packed must be 256-byte aligned");
+  int rc = check_dtype(weight_dtype);
+  if (rc != B200TA_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* base = static_cast<char*>(packed);
+  B200TA_CHECK_CUDA(cudaMemsetAsync(base, 0, kNodePackBytes, s));
+  // rows 0..511 (q, k, v, g of a triangle node) stay zero; the bias heads follow
+  constexpr int kFirst = 4 * kHeads * kHeadDim;
+  fold_rows_kernel<<<kNodeRows, kC, 0, s>>>(
+      nullptr, kFirst, w_z, num_heads, nullptr, ln_w, ln_b, weight_dtype, kFirst, kFirst + num_heads, bias_scale,
+      reinterpret_cast<__nv_bfloat16*>(base + kNodeWOff), reinterpret_cast<float2*>(base + kNodeScOff),
+      reinterpret_cast<int*>(base + kNodeFlagsOff));
   B200TA_CHECK_CUDA(cudaGetLastError());
   return B200TA_OK;
 }

@@ -3,11 +3,12 @@
 from .attention_backend import (AttentionBackend, AttentionMetadata, AttentionType, B200TriangleAttention,
                                 PrecomputedPairMasks, create_attention, get_attention_backend, mask_to_lengths,
                                 precompute_pair_masks, register_precompute_pair_masks)
+from .attention_pair_bias import AttentionPairBias
 from .auto_chunk import (CHUNK_REGISTRY, PAIR_TRANSITION, TRIANGLE_ATTENTION, ChunkPolicy, chunk_apply,
                          default_autochunk_min, iter_chunks)
 from .buffers import PreallocatedBuffers, ensure_buffer
 from .linear import Linear, WeightMode, WeightsLoadingConfig
-from .pairformer import PairformerNoSeqLayer, PairformerNoSeqModule
+from .pairformer import PairformerLayerV1, PairformerModule, PairformerNoSeqLayer, PairformerNoSeqModule
 from .transition import Transition
 from .triangle_multiplication import (TriangleMultiplicationMetadata, TriangleMultiplicationNode,
                                       TriangleMultiplicationNodeType, precompute_trimul_metadata,
@@ -24,4 +25,5 @@ __all__ = [
     "TriangleAttentionNode", "TriangleAttentionNodeType", "TriangleAttentionStartingNode", "split_pair_bias_proj",
     "TriangleMultiplicationMetadata", "TriangleMultiplicationNode", "TriangleMultiplicationNodeType",
     "precompute_trimul_metadata", "set_trimul_token_padding", "PairformerNoSeqLayer", "PairformerNoSeqModule",
+    "AttentionPairBias", "PairformerLayerV1", "PairformerModule",
 ]

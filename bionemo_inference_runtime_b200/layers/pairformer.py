@@ -1,11 +1,13 @@
-"""Pair-track Pairformer blocks on the sm_100a kernels.
+"""Pairformer blocks on the sm_100a kernels.
 
-Counterparts of ``PairformerNoSeqLayer`` and ``PairformerNoSeqModule``
-(``bionemo_ir/_torch/layers/transformers/pairformer.py:255-363``), the reference's Pairformer without the single
-track: per block triangle multiplication outgoing and incoming, triangle attention starting and ending node and the
-pair transition, every update added to ``z`` (``_transform_z``, lines 174-216 of the same file).  Submodule names
-(``tri_mul_out``, ``tri_mul_in``, ``tri_attn_start``, ``tri_attn_end``, ``transition_z``) and therefore the
-``state_dict`` keys are the reference's, so the pair-track part of a Pairformer checkpoint loads unchanged.
+Counterparts of ``PairformerLayerV1``, ``PairformerNoSeqLayer``, ``PairformerNoSeqModule`` and ``PairformerModule``
+(``bionemo_ir/_torch/layers/transformers/pairformer.py:44-363`` and ``418-510``).  Per block the pair track runs
+triangle multiplication outgoing and incoming, triangle attention starting and ending node and the pair
+transition, every update added to ``z`` (``_transform_z``, lines 174-216 of the same file); the single track
+(``PairformerLayerV1.forward``, lines 218-252) then adds the attention with pair bias and the single transition to
+``s``.  Submodule names (``attention``, ``tri_mul_out``, ``tri_mul_in``, ``tri_attn_start``, ``tri_attn_end``,
+``transition_s``, ``transition_z``) and therefore the ``state_dict`` keys are the reference's, so a Pairformer
+checkpoint loads unchanged.
 
 The module can replay its whole stack from one CUDA graph (``use_cuda_graph=True``): at 15 kernel launches per block
 the launch overhead is what the reference removes with graph capture at small token counts
@@ -18,6 +20,7 @@ import torch
 import torch.nn as nn
 
 from .attention_backend import AttentionMetadata, PrecomputedPairMasks, precompute_pair_masks
+from .attention_pair_bias import AttentionPairBias
 from .auto_chunk import CHUNK_REGISTRY, PAIR_TRANSITION
 from .buffers import PreallocatedBuffers
 from .transition import Transition
@@ -26,20 +29,33 @@ from .triangle_multiplication import (TriangleMultiplicationMetadata, TriangleMu
 from .triangle_nodes import TriangleAttentionEndingNode, TriangleAttentionStartingNode
 
 
-class PairformerNoSeqLayer(nn.Module):
-    def __init__(self, *, layer_idx: int, token_z: int = 128, pairwise_head_width: int = 32, pairwise_num_heads: int = 4,
-                 dtype: torch.dtype = None, eps: float = 1e-5, inf: float = 1e9, triangle_attn_backend: str = "VANILLA",
-                 skip_create_weights: bool = False, trimul_high_precision: bool = True,
+class PairformerLayerV1(nn.Module):
+    def __init__(self, layer_idx: int = 0, token_s: int = 384, token_z: int = 128, num_heads: int = 16,
+                 pairwise_head_width: int = 32, pairwise_num_heads: int = 4, no_update_s: bool = False,
+                 no_update_z: bool = False, dtype: torch.dtype = None, eps: float = 1e-5, inf: float = 1e9,
+                 triangle_attn_backend: str = "VANILLA", pairwise_attn_backend: str = "VANILLA",
+                 skip_create_weights: bool = False, attention_initial_norm: bool = False,
+                 s_path_dtype: str | torch.dtype | None = None, trimul_high_precision: bool = True,
                  trimul_mean_normalization: bool = False, pair_mask_left_aligned: bool = True,
                  pair_transition_factor: int = 4, tri_attn_transposed_bias: bool = False, **kwargs):
-        """Arguments as the reference layer takes them for its pair track (pairformer.py:45-67); arguments of the
-        single track (``token_s``, ``num_heads``, ``pairwise_attn_backend``, ...) are accepted and unused."""
+        """Arguments as the reference layer takes them (pairformer.py:45-67).  ``s_path_dtype`` other than bfloat16
+        is accepted and the single track still computes in bfloat16 (fp32 accumulation), returning ``s`` in the
+        dtype it came in."""
         super().__init__()
+        if no_update_z:
+            raise ValueError("no_update_z is not supported: the pair track is the purpose of these kernels")
         self.dtype = dtype
-        self.no_update_s, self.no_update_z = True, False
-        self.token_z = token_z
+        self.no_update_s, self.no_update_z = no_update_s, False
+        self.token_s, self.token_z = token_s, token_z
         self.triangle_attn_backend = triangle_attn_backend
+        self.pairwise_attn_backend = pairwise_attn_backend
         self.pair_mask_left_aligned = pair_mask_left_aligned
+        self.s_path_dtype = s_path_dtype if s_path_dtype is not None else dtype
+        if not no_update_s:
+            self.attention = AttentionPairBias(layer_idx=layer_idx, c_s=token_s, c_z=token_z, num_heads=num_heads,
+                                               dtype=torch.bfloat16, bias_proj=True, eps=eps, inf=inf,
+                                               skip_create_weights=skip_create_weights,
+                                               attn_backend=pairwise_attn_backend, initial_norm=attention_initial_norm)
 
         def trimul(kind):
             return TriangleMultiplicationNode(layer_idx=layer_idx, dim=token_z, eps=eps, multiplication_type=kind,
@@ -55,14 +71,17 @@ class PairformerNoSeqLayer(nn.Module):
         self.tri_attn_start = TriangleAttentionStartingNode(token_z, pairwise_head_width, pairwise_num_heads, **node_kw)
         self.tri_attn_end = TriangleAttentionEndingNode(token_z, pairwise_head_width, pairwise_num_heads,
                                                         transposed_bias=tri_attn_transposed_bias, **node_kw)
+        if not no_update_s:
+            self.transition_s = Transition(token_s, token_s * 4, layer_idx=layer_idx, eps=eps, dtype=torch.bfloat16,
+                                           skip_create_weights=skip_create_weights)
         self.transition_z = Transition(token_z, token_z * pair_transition_factor, layer_idx=layer_idx, eps=eps,
                                        dtype=dtype, skip_create_weights=skip_create_weights,
                                        auto_chunk_policy=CHUNK_REGISTRY.get(PAIR_TRANSITION))
 
-    def forward(self, z: torch.Tensor, pair_mask: torch.Tensor, trimul_metadata: TriangleMultiplicationMetadata,
-                attn_metadatas: dict[str, AttentionMetadata] | None = None,
-                precomputed_masks: PrecomputedPairMasks | None = None, precomputed_single_masks=None,
-                buffers: PreallocatedBuffers | None = None, inplace_safe: bool = False, **kwargs) -> torch.Tensor:
+    def _transform_z(self, z: torch.Tensor, pair_mask: torch.Tensor, trimul_metadata: TriangleMultiplicationMetadata,
+                     attn_metadatas: dict[str, AttentionMetadata] | None = None,
+                     precomputed_masks: PrecomputedPairMasks | None = None,
+                     buffers: PreallocatedBuffers | None = None, inplace_safe: bool = False) -> torch.Tensor:
         can_update_inplace = inplace_safe and not torch.cuda.is_current_stream_capturing()
         z = self.tri_mul_out(z, mask=pair_mask, trimul_metadata=trimul_metadata, residual=True, buffers=buffers)
         z = self.tri_mul_in(z, mask=pair_mask, trimul_metadata=trimul_metadata, residual=True, buffers=buffers)
@@ -77,6 +96,86 @@ class PairformerNoSeqLayer(nn.Module):
             z = node(z, mask=pair_mask, mask_bias=node_mask_bias, attn_metadata=tri_attn_metadata, buffers=buffers,
                      residual=True, inplace_residual=can_update_inplace)
         return self.transition_z(z, residual=True, inplace=True)
+
+    def forward(self, s: torch.Tensor, z: torch.Tensor, mask: torch.Tensor, pair_mask: torch.Tensor,
+                trimul_metadata: TriangleMultiplicationMetadata,
+                attn_metadatas: dict[str, AttentionMetadata] | None = None,
+                precomputed_masks: PrecomputedPairMasks | None = None, precomputed_single_masks=None,
+                buffers: PreallocatedBuffers | None = None, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
+        z = self._transform_z(z, pair_mask, trimul_metadata, attn_metadatas, precomputed_masks=precomputed_masks,
+                              buffers=buffers, inplace_safe=bool(kwargs.get("inplace_safe", False)))
+        if not self.no_update_s:
+            mask_bias = getattr(precomputed_single_masks, "mask_bias", None)
+            s_dtype = s.dtype
+            # attention(..., residual=s) is the reference's ``s + attention(s, z, mask)`` with the add in the
+            # output-projection kernel; the result is a fresh tensor, so the transition updates it in place
+            s = self.attention(s, z, mask, attn_metadata=(attn_metadatas or {}).get("pairwise_attn"),
+                               mask_bias=mask_bias, buffers=buffers, residual=s)
+            s = self.transition_s(s.to(torch.bfloat16), residual=True, inplace=True).to(s_dtype)
+        return s, z
+
+
+class PairformerNoSeqLayer(PairformerLayerV1):
+    def __init__(self, *, layer_idx: int, **kwargs):
+        """The layer without the single track (pairformer.py:255-306); arguments as :class:`PairformerLayerV1`."""
+        kwargs.pop("no_update_s", None)
+        super().__init__(layer_idx=layer_idx, no_update_s=True, **kwargs)
+
+    def forward(self, z: torch.Tensor, pair_mask: torch.Tensor, trimul_metadata: TriangleMultiplicationMetadata,
+                attn_metadatas: dict[str, AttentionMetadata] | None = None,
+                precomputed_masks: PrecomputedPairMasks | None = None, precomputed_single_masks=None,
+                buffers: PreallocatedBuffers | None = None, inplace_safe: bool = False, **kwargs) -> torch.Tensor:
+        return self._transform_z(z, pair_mask, trimul_metadata, attn_metadatas, precomputed_masks=precomputed_masks,
+                                 buffers=buffers, inplace_safe=inplace_safe)
+
+
+class PairformerModule(nn.Module):
+    """The stack with the single track (pairformer.py:418-510).  The reference builds it from a config object;
+    here the same fields are keyword arguments (``num_blocks``, ``token_s``, ``token_z``, ``num_heads``, ...), or a
+    ``config`` object carrying them under the reference's names."""
+
+    _CONFIG_FIELDS = {"num_blocks": "num_blocks", "token_s": "token_s", "token_z": "token_z", "num_heads": "num_heads",
+                      "pairwise_head_width": "pairwise_head_width", "pairwise_num_heads": "pairwise_num_heads",
+                      "no_update_s": "no_update_s", "torch_dtype": "dtype", "norm_epsilon": "eps", "mask_inf": "inf",
+                      "skip_create_weights": "skip_create_weights",
+                      "triangle_attention_backend": "triangle_attn_backend",
+                      "pairwise_attention_backend": "pairwise_attn_backend",
+                      "attention_initial_norm": "attention_initial_norm",
+                      "trimul_high_precision": "trimul_high_precision",
+                      "trimul_mean_normalization": "trimul_mean_normalization", "s_path_dtype": "s_path_dtype",
+                      "tri_attn_transposed_bias": "tri_attn_transposed_bias"}
+
+    def __init__(self, config=None, **kwargs):
+        super().__init__()
+        if config is not None:
+            if getattr(config, "version", "v1") != "v1":
+                raise ValueError("only the v1 pairformer layer is built on the sm_100a kernels")
+            for field, name in self._CONFIG_FIELDS.items():
+                if hasattr(config, field):
+                    kwargs.setdefault(name, getattr(config, field))
+        num_blocks = kwargs.pop("num_blocks", 8)
+        self.config = config
+        self.layers = nn.ModuleList([PairformerLayerV1(layer_idx=i, **kwargs) for i in range(num_blocks)])
+        self.pair_mask_left_aligned = self.layers[0].pair_mask_left_aligned if self.layers else False
+
+    def forward(self, s: torch.Tensor, z: torch.Tensor, mask: torch.Tensor, pair_mask: torch.Tensor,
+                attn_metadatas: dict[str, AttentionMetadata] | None = None,
+                buffers: PreallocatedBuffers | None = None, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
+        if not self.layers:
+            return s, z
+        first = self.layers[0]
+        precomputed = precompute_pair_masks(first.triangle_attn_backend, pair_mask, inf=first.tri_attn_start.inf,
+                                            dtype=first.dtype)
+        if buffers is None:
+            buffers = {}
+        int_lengths = precomputed.mask_bias.dtype == torch.int32
+        trimul_metadata = precompute_trimul_metadata(
+            z, precomputed.mask_bias if int_lengths else None,
+            precomputed.mask_bias_transposed if int_lengths else None, enabled=self.pair_mask_left_aligned)
+        for layer in self.layers:
+            s, z = layer(s, z, mask, pair_mask, trimul_metadata, attn_metadatas, precomputed_masks=precomputed,
+                         buffers=buffers, **kwargs)
+        return s, z
 
 
 class PairformerNoSeqModule(nn.Module):

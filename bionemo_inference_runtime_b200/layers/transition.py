@@ -3,9 +3,12 @@
 Drop-in counterpart of ``Transition`` (``bionemo_ir/_torch/layers/transition.py:187-336``): same constructor,
 ``forward(x, mask=None, *, residual=False, inplace=False)``, ``post_load_weights()`` and ``state_dict`` keys
 (``norm.{weight,bias}``, ``fused_fc2_fc1.weight`` with value rows first and gate rows second, ``fc3.weight``).
-The reference picks between three paths per call; here every call is the one fused kernel
-(``b200ta_transition``), which already does what the reference's ``transition_mlp_w_norm`` path does:
-LayerNorm folded into the first linear, hidden activation kept on chip, mask and residual in the epilogue.
+The reference picks between three paths per call; here every call of the pair transition (dim 128, hidden 512) is
+the one fused kernel (``b200ta_transition``), which already does what the reference's ``transition_mlp_w_norm``
+path does: LayerNorm folded into the first linear, hidden activation kept on chip, mask and residual in the
+epilogue.  Other widths (the single-track transition, dim 384 and hidden 1536) run as row statistics plus two
+tensor-core GEMMs (``b200ta_linear``): LayerNorm folded into the first, SwiGLU in its epilogue, the residual in
+the epilogue of the second.
 """
 
 from __future__ import annotations
@@ -36,9 +39,11 @@ class Transition(nn.Module):
         super().__init__()
         if out_dim is None:
             out_dim = dim
-        if (dim, hidden, out_dim) != (ops.C, ops.HIDDEN, ops.C):
-            raise ValueError(f"the sm_100a transition kernel is specialised for dim={ops.C}, hidden={ops.HIDDEN}, "
-                             f"out_dim={ops.C}; got ({dim}, {hidden}, {out_dim})")
+        self._fused = (dim, hidden, out_dim) == (ops.C, ops.HIDDEN, ops.C)
+        if not self._fused and (out_dim != dim or dim % 128 or hidden % 128 or dim > 2048):
+            raise ValueError(f"the sm_100a transition kernels take dim={ops.C}, hidden={ops.HIDDEN} (fused) or "
+                             f"multiples of 128 with dim <= 2048 and out_dim == dim; got ({dim}, {hidden}, {out_dim})")
+        self.dim = dim
         self.auto_chunk_policy = auto_chunk_policy  # accepted; the fused kernel holds no activation beyond its output
         self.normalize = normalize
         self.dtype = dtype
@@ -63,14 +68,28 @@ class Transition(nn.Module):
         if not (self.fused_fc2_fc1._weights_created and self.fc3._weights_created) or not self.fc3.weight.is_cuda:
             self._pack = self._pack_state = None
             return
-        dev = self.fc3.weight.device
-        self._pack = ops.pack_transition_weights(*[None if p is None else p.to(dev) for p in self._params()])
+        self._pack = self._fold(self.fc3.weight.device)
         self._pack_state = _weight_state(*self._params())
+
+    @torch.no_grad()
+    def _fold(self, device):
+        params = [None if p is None else p.detach().to(device) for p in self._params()]
+        if self._fused:
+            return ops.pack_transition_weights(*params)
+        from .attention_pair_bias import fold_linear
+
+        ln_w, ln_b, w1, w2 = params
+        # value rows first, gate rows second -> groups of 32 rows: 16 values followed by their 16 gates
+        value, gate = w1.float().reshape(2, self.hidden // 16, 16, self.dim)
+        w1_f, sc1 = fold_linear(torch.cat([value, gate], dim=1).reshape(2 * self.hidden, self.dim), None, ln_w, ln_b)
+        w2_f, sc2 = fold_linear(w2, None, None, None)
+        return {"w1": w1_f, "sc1": sc1, "w2": w2_f, "sc2": sc2}
 
     def _packed(self, device) -> torch.Tensor:
         state = _weight_state(*self._params())
-        if self._pack is None or self._pack.device != device or state != self._pack_state:
-            pack = ops.pack_transition_weights(*[None if p is None else p.to(device) for p in self._params()])
+        held = self._pack["w1"] if isinstance(self._pack, dict) else self._pack
+        if held is None or held.device != device or state != self._pack_state:
+            pack = self._fold(device)
             if not torch.cuda.is_current_stream_capturing():
                 self._pack, self._pack_state = pack, state
             return pack
@@ -89,11 +108,29 @@ class Transition(nn.Module):
             x = x.to(torch.bfloat16)
             inplace = False
         xc = x if x.is_contiguous() else x.contiguous()
+        if not self._fused:
+            return self._forward_gemms(x, xc, mask, residual, inplace)
         out = xc if (residual and inplace and xc is x) else None
         row_mask = None if mask is None else _row_mask(xc, mask)
         y = ops.transition(xc, self._packed(x.device), row_mask, self.eps if self.norm is None else self.norm.eps,
                            residual=residual, out=out)
         if residual and inplace and y is not x:
+            x.copy_(y)
+            return x
+        return y
+
+    def _forward_gemms(self, x, xc, mask, residual: bool, inplace: bool) -> torch.Tensor:
+        if mask is not None:
+            raise ValueError("a row mask is only supported by the fused pair transition (dim 128, hidden 512)")
+        w = self._packed(x.device)
+        rows = xc.numel() // self.dim
+        eps = self.eps if self.norm is None else self.norm.eps
+        stats = ops.row_stats(xc, eps) if self.norm is not None else None
+        h = ops.linear(xc, w["w1"], w["sc1"], ops.LINEAR_SWIGLU, B=1, rows=rows, stats=stats)
+        x3 = xc.view(1, rows, self.dim)
+        y = ops.linear(h, w["w2"], w["sc2"], ops.LINEAR_ROWS, B=1, rows=rows, residual=x3 if residual else None,
+                       out=x3 if (residual and inplace) else None).view(xc.shape)
+        if residual and inplace and xc is not x:
             x.copy_(y)
             return x
         return y

@@ -356,3 +356,93 @@ def trimul_output(z: torch.Tensor, x: torch.Tensor, packed: torch.Tensor, eps: f
     _lib.call("b200ta_trimul_output", z.data_ptr(), sb, si, sj, x.data_ptr(), x.shape[-1], _ptr(mask), *ms,
               packed.data_ptr(), float(eps), 1 if residual else 0, out.data_ptr(), osb, osi, osj, B, I, _stream())
     return out
+
+
+# ---- single track: pair bias and dense layers ---------------------------------------------------------------------
+
+LINEAR_PLANES, LINEAR_ROWS, LINEAR_SWIGLU = 0, 1, 2
+SINGLE_HEADS = 16  # heads of the single-track attention the head-major form of ``linear`` writes
+
+
+def pack_pair_bias_weights(ln_w, ln_b, w_z: torch.Tensor, bias_scale: float) -> torch.Tensor:
+    """Fold LayerNorm into the pair-bias projection ``w_z [heads, 128]``; the result is multiplied by ``bias_scale``."""
+    ts = [_contig(t) for t in (ln_w, ln_b, w_z)]
+    heads = ts[2].shape[0]
+    if ts[2].dim() != 2 or ts[2].shape[1] != C or not 0 < heads <= 16 or heads % 2:
+        raise ValueError(f"the pair-bias kernel takes an even number of at most 16 heads over c_z={C}; got {tuple(ts[2].shape)}")
+    dt = _weight_dtype(*ts)
+    packed = torch.empty(_lib.load().b200ta_node_pack_bytes(), dtype=torch.uint8, device=ts[2].device)
+    _lib.call("b200ta_pack_pair_bias_weights", _ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]), heads, float(bias_scale), dt,
+              packed.data_ptr(), _stream())
+    return packed
+
+
+def pair_bias(z: torch.Tensor, packed: torch.Tensor, heads: int, eps: float = 1e-5,
+              bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``bias[b, h, q, k] = scale * LayerNorm(z[b, q, k]) · w_z[h]`` as ``[B, heads, Q, pad8(K)]`` (pad written as 0)."""
+    _require_cuda_bf16("z", z)
+    B, Q, K, sb, sq, sk = _pair_strides(z, False)
+    if bias is None:
+        bias = torch.empty((B, heads, Q, pad8(K)), dtype=torch.bfloat16, device=z.device)
+    _require_cuda_bf16("bias", bias)
+    if tuple(bias.shape) != (B, heads, Q, pad8(K)):
+        raise ValueError(f"bias must have shape {(B, heads, Q, pad8(K))}, got {tuple(bias.shape)}")
+    _lib.call("b200ta_pair_bias", z.data_ptr(), sb, sq, sk, packed.data_ptr(), float(eps), bias.data_ptr(),
+              *bias.stride(), heads, B, Q, K, pad8(K), _stream())
+    return bias
+
+
+def row_stats(x: torch.Tensor, eps: float = 1e-5, stats: torch.Tensor | None = None) -> torch.Tensor:
+    """LayerNorm statistics ``{rstd, -mean * rstd}`` of every row of ``x [..., K]`` (contiguous bf16) as ``[rows, 2]``."""
+    _require_cuda_bf16("x", x)
+    if not x.is_contiguous():
+        raise ValueError("row_stats needs a contiguous tensor")
+    K = x.shape[-1]
+    rows = x.numel() // K
+    if stats is None:
+        stats = torch.empty((rows, 2), dtype=torch.float32, device=x.device)
+    _lib.call("b200ta_row_stats", x.data_ptr(), K, rows, K, float(eps), stats.data_ptr(), _stream())
+    return stats
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, sc: torch.Tensor, mode: int, *, B: int, rows: int,
+           a_strides: tuple[int, int, int] | None = None, stats: torch.Tensor | None = None,
+           residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``finish(A · wᵀ)`` on the tensor cores (``b200ta_linear``).
+
+    ``a``: bf16 ``[B, rows, K]`` contiguous, or any layout with ``a_strides = (batch, row, 128-channel chunk)`` in
+    elements; ``w``: bf16 ``[N, K]``; ``sc``: fp32 ``[N, 2]`` {rowsum, const}; ``stats`` from :func:`row_stats`.
+    Returns ``[4, B, 16, rows, 32]`` (``LINEAR_PLANES``), ``[B, rows, N]`` (``LINEAR_ROWS``, plus ``residual``) or
+    ``[B, rows, N // 2]`` (``LINEAR_SWIGLU``).
+    """
+    _require_cuda_bf16("a", a)
+    _require_cuda_bf16("w", w)
+    N, K = w.shape
+    if not w.is_contiguous() or sc.dtype != torch.float32 or tuple(sc.shape) != (N, 2) or not sc.is_contiguous():
+        raise ValueError("w must be contiguous [N, K] and sc a contiguous fp32 [N, 2]")
+    if a_strides is None:
+        if not a.is_contiguous() or a.numel() != B * rows * K:
+            raise ValueError(f"a must be a contiguous [B={B}, rows={rows}, K={K}] tensor, got {tuple(a.shape)}")
+        a_strides = (rows * K, K, C)
+    if mode == LINEAR_PLANES:
+        shape = (4, B, SINGLE_HEADS, rows, HEAD_DIM)
+    elif mode == LINEAR_ROWS:
+        shape = (B, rows, N)
+    elif mode == LINEAR_SWIGLU:
+        shape = (B, rows, N // 2)
+    else:
+        raise ValueError(f"unknown mode {mode}")
+    if out is None:
+        out = torch.empty(shape, dtype=torch.bfloat16, device=a.device)
+    _require_cuda_bf16("out", out)
+    if tuple(out.shape) != shape or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous tensor of shape {shape}")
+    if residual is not None:
+        _require_cuda_bf16("residual", residual)
+        if tuple(residual.shape) != shape or not residual.is_contiguous():
+            raise ValueError(f"residual must be a contiguous tensor of shape {shape}")
+    os_row = 0 if mode == LINEAR_PLANES else shape[-1]
+    plane_stride = out.stride(0) if mode == LINEAR_PLANES else 0
+    _lib.call("b200ta_linear", a.data_ptr(), *a_strides, w.data_ptr(), sc.data_ptr(), _ptr(stats), _ptr(residual),
+              0 if residual is None else shape[-1], out.data_ptr(), os_row, plane_stride, mode, B, rows, K, N, _stream())
+    return out

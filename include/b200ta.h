@@ -121,6 +121,26 @@ int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
                     int64_t bs_q, int64_t bs_k, int B, int R, int S, int S_pad, void* stream);
 
 /*
+ * Pair bias of the single-track attention: bias[b,h,q,k] = bias_scale * ( LayerNorm(z[b,q,k,:]) · W_z[h,:] ) for up
+ * to 16 heads, written head-major with the key axis padded: the projection, the moveaxis and the padding in one pass
+ * over z (the prologue kernel in its bias-only form, one N=16 tcgen05 GEMM per 128-position tile).
+ *
+ *   b200ta_pack_pair_bias_weights: ln_w, ln_b [128] (both NULL: z is used as it is), w_z [num_heads,128] in
+ *       weight_dtype; bias_scale multiplies the result (pass 1/softmax_scale for b200ta_attention);
+ *       packed: b200ta_node_pack_bytes() bytes, 256-byte aligned.
+ *   b200ta_pair_bias: z [B,Q,K,128] bf16 via element strides; bias at b*bs_b + h*bs_h + q*bs_q + k*bs_k;
+ *       entries K <= k < K_pad are written as zero; num_heads even, at most 16.
+ *
+ * Replaces: LNProjMoveaxisPad.forward (bionemo_ir/_torch/custom_ops/fused_ln_proj_moveaxis_pad.py:90-154), as
+ * AttentionPairBias.project_pair_bias calls it (bionemo_ir/_torch/layers/attention.py:835-852).
+ */
+int b200ta_pack_pair_bias_weights(const void* ln_w, const void* ln_b, const void* w_z, int num_heads,
+                                  float bias_scale, int weight_dtype, void* packed, void* stream);
+int b200ta_pair_bias(const void* z, int64_t zs_b, int64_t zs_q, int64_t zs_k, const void* packed, float eps,
+                     void* bias, int64_t bs_b, int64_t bs_h, int64_t bs_q, int64_t bs_k, int num_heads,
+                     int B, int Q, int K, int K_pad, void* stream);
+
+/*
  * Attention core.  For every (b, r, h) and query s:
  *   o[s,:] = softmax_t( scale * (q[s]·k[t] + bias[b,h,s,t]) ; t < len[b,r] ) · v[t,:]
  * optionally multiplied by gate[s,:], the gate factors in [0,1] (sigmoid already applied, as
@@ -243,6 +263,38 @@ int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* p
 int b200ta_transition_scatter(const void* x, const void* mask, const void* packed, float eps,
                               void* const* peer_out, int num_peers, int rank, int B, int tokens, int cols,
                               int add_residual, void* stream);
+
+/* ---- dense layers of the single track ---------------------------------------------------
+ *
+ * The single representation s[B, tokens, 384] has one row per token; its layers are small GEMMs.
+ *
+ * b200ta_row_stats: {rstd, -mean*rstd} (two floats) of every row of x[rows, K] (bf16, row stride in elements):
+ *     the LayerNorm statistics b200ta_linear applies to a GEMM whose weights have the LayerNorm folded in.
+ *
+ * b200ta_linear: out = finish(A · Wᵀ) on the tensor cores, one 128x128 tile per CTA.
+ *     A      bf16, element (b, row, k) at b*as_b + row*as_row + (k / 128)*as_chunk + k % 128 (a row-major matrix
+ *            has as_chunk = 128; the attention output [B, 4, rows, 128] is read in place with as_chunk = rows*128).
+ *     w      bf16 [N, K] row-major; K, N multiples of 128.
+ *     sc     float [N][2] {rowsum, const}: value[n] = rstd*acc[n] + nmr*rowsum[n] + const[n] with {rstd, nmr} the
+ *            row's entry of `stats` ([B*rows][2]) or {1, 0} when stats is NULL.
+ *     mode   B200TA_LINEAR_PLANES: N = 2048 columns ordered (which, head, 32) are written head-major as
+ *                [which][B][16][rows][32] (plane_stride elements between planes), plane 3 as sigmoid(value): the
+ *                q, k, v and gate operands of b200ta_attention;
+ *            B200TA_LINEAR_ROWS: out[(b*rows + row)*os_row + n] = value[n] (+ residual, same indexing with rs_row);
+ *            B200TA_LINEAR_SWIGLU: every 32 columns are 16 values followed by their 16 gates;
+ *                out[(b*rows + row)*os_row + n/2 + j] = silu(gate_j) * value_j.
+ *
+ * Replaces: the eager projections of AttentionPairBias (in_proj, proj_o; bionemo_ir/_torch/layers/attention.py:
+ * 764-805 and 1099-1132) and of the single-track Transition (bionemo_ir/_torch/layers/transformers/
+ * pairformer.py:153-160), which the reference runs through cuBLAS and Triton element-wise kernels.
+ */
+#define B200TA_LINEAR_PLANES 0
+#define B200TA_LINEAR_ROWS 1
+#define B200TA_LINEAR_SWIGLU 2
+int b200ta_row_stats(const void* x, int64_t row_stride, int64_t rows, int K, float eps, void* stats, void* stream);
+int b200ta_linear(const void* a, int64_t as_b, int64_t as_row, int64_t as_chunk, const void* w, const void* sc,
+                  const void* stats, const void* residual, int64_t rs_row, void* out, int64_t os_row,
+                  int64_t plane_stride, int mode, int B, int rows, int K, int N, void* stream);
 
 /* ---- triangle multiplication ---------------------------------------------------------
  *

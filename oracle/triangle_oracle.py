@@ -333,3 +333,72 @@ def trimul_forward(z: torch.Tensor, mask: torch.Tensor | None, w: TriMulWeights,
     (triangle_nodes.py:723-727: the unfused path adds the residual without masking it)."""
     st = trimul_stages(z, mask, w, direction, **kw)
     return z.to(st["update"].dtype) + st["update"] if residual else st["update"]
+
+
+# ------------------------------------------------------------------------------- single track: attention with pair bias
+
+
+@dataclass
+class PairBiasAttentionWeights:
+    """Parameters of AttentionPairBias as the pairformer builds it (state_dict names in brackets)."""
+
+    norm_s_w: torch.Tensor | None  # [c_s]        (norm_s.weight; None without initial_norm)
+    norm_s_b: torch.Tensor | None  # [c_s]        (norm_s.bias)
+    w_in: torch.Tensor             # [4*c_s, c_s] (in_proj.weight; rows ordered q, gate, k, v)
+    b_in: torch.Tensor             # [4*c_s]      (in_proj.bias)
+    norm_z_w: torch.Tensor         # [c_z]        (proj_z.0.weight)
+    norm_z_b: torch.Tensor         # [c_z]        (proj_z.0.bias)
+    w_z: torch.Tensor              # [H, c_z]     (proj_z.1.weight)
+    w_o: torch.Tensor              # [c_s, c_s]   (proj_o.weight)
+    b_o: torch.Tensor | None = None  # [c_s]      (proj_o.bias, with out_bias)
+
+    def to(self, dtype: torch.dtype) -> "PairBiasAttentionWeights":
+        return PairBiasAttentionWeights(*[None if t is None else t.to(dtype) for t in self.__dict__.values()])
+
+
+def make_pair_bias_attention_weights(seed: int, c_s: int = 384, c_z: int = 128, heads: int = 16, std: float = 0.05,
+                                     initial_norm: bool = True, out_bias: bool = False) -> PairBiasAttentionWeights:
+    g = torch.Generator().manual_seed(seed)
+    w_in = torch.randn(4 * c_s, c_s, generator=g) * std
+    b_in = torch.randn(4 * c_s, generator=g) * 0.1
+    w_z = torch.randn(heads, c_z, generator=g) * std
+    w_o = torch.randn(c_s, c_s, generator=g) * std
+    norm_z_w = 1 + 0.2 * torch.randn(c_z, generator=g)
+    norm_z_b = 0.2 * torch.randn(c_z, generator=g)
+    norm_s_w = 1 + 0.2 * torch.randn(c_s, generator=g) if initial_norm else None
+    norm_s_b = 0.2 * torch.randn(c_s, generator=g) if initial_norm else None
+    b_o = 0.1 * torch.randn(c_s, generator=g) if out_bias else None
+    return PairBiasAttentionWeights(norm_s_w, norm_s_b, w_in, b_in, norm_z_w, norm_z_b, w_z, w_o, b_o)
+
+
+def pair_bias_attention_forward(s: torch.Tensor, z: torch.Tensor, mask: torch.Tensor, w: PairBiasAttentionWeights, *,
+                                heads: int = 16, inf: float = 1e9, eps: float = 1e-5) -> torch.Tensor:
+    """The update of the single representation ``s [B, N, c_s]`` by self-attention with a bias from ``z [B, N, N, c_z]``.
+
+    Reference: AttentionPairBias.forward without AdaLN, key gathering or output gate
+    (bionemo_ir/_torch/layers/attention.py:957-1046): initial LayerNorm (_prep_inputs), ``q, g, k, v = in_proj(s)``
+    (_prep_qkvg, lines 790-792), pair bias ``moveaxis(Linear(LayerNorm(z)))`` (project_pair_bias, lines 835-852;
+    LNProjMoveaxisPad, bionemo_ir/_torch/custom_ops/fused_ln_proj_moveaxis_pad.py:15-22), additive key mask
+    ``(1 - mask) * -inf`` (_prep_mask_bias, lines 917-921), ``softmax(q·kᵀ / sqrt(d) + mask + bias) · v``
+    (VanillaPairwiseAttention.forward, bionemo_ir/_torch/attention_backend/pairwise_attention/vanilla.py:59-77) and
+    ``proj_o(sigmoid(g) * o)`` (_attention_output, lines 1114-1119).
+    """
+    dtype = w.w_in.dtype
+    B, N, c_s = s.shape
+    d = c_s // heads
+    x = s.to(dtype)
+    if w.norm_s_w is not None:
+        x = F.layer_norm(x, (c_s,), w.norm_s_w, w.norm_s_b, eps)
+    q, g, k, v = F.linear(x, w.w_in, w.b_in).split(c_s, dim=-1)
+    zn = F.layer_norm(z.to(dtype), (z.shape[-1],), w.norm_z_w, w.norm_z_b, eps)
+    pair_bias = F.linear(zn, w.w_z).movedim(-1, -3)  # [B, H, N, N]
+    mask_bias = ((1 - mask.float()) * -inf)[:, None, None, :]
+
+    def heads_first(t):
+        return t.reshape(B, N, heads, d).transpose(1, 2)  # [B, H, N, d]
+
+    a = torch.matmul(heads_first(q), heads_first(k).transpose(-1, -2)) / math.sqrt(d)
+    a = a + mask_bias.to(dtype) + pair_bias
+    a = torch.softmax(a, dim=-1)
+    o = torch.matmul(a, heads_first(v)).transpose(1, 2).reshape(B, N, c_s)
+    return F.linear(o * torch.sigmoid(g), w.w_o, w.b_o)

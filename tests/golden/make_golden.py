@@ -169,6 +169,76 @@ def main() -> None:
          out_module_update_masked_bf16=mod_upd16, **{f"w_{k}": v for k, v in tw.items()})
 
     trimul_cases()
+    single_track_cases()
+
+
+def single_track_cases() -> None:
+    """Single-track attention with pair bias and the single-track transition.  The reference's AttentionPairBias runs
+    in eager mode on CPU except for its pair-bias projection (LNProjMoveaxisPad launches Triton kernels): that one
+    submodule is replaced by the three PyTorch operations it documents (LayerNorm + Linear through the layer's own
+    ``proj_z``, moveaxis(-1, -3), no padding); everything else is the reference's code."""
+    from bionemo_ir._torch.layers.attention import AttentionPairBias
+    from bionemo_ir._torch.layers.transition import Transition
+
+    class EagerPairBias(torch.nn.Module):
+        def forward(self, z, **kw):
+            return kw["proj_z"](z).movedim(-1, -3).contiguous()
+
+    def build(dtype, w, initial_norm, out_bias):
+        layer = AttentionPairBias(layer_idx=0, c_s=384, c_z=128, num_heads=16, dtype=dtype, bias_proj=True, inf=1e9,
+                                  skip_create_weights=True, attn_backend="VANILLA", initial_norm=initial_norm,
+                                  out_bias=out_bias)
+        if initial_norm:
+            layer.norm_s.weight.data.copy_(w["norm_s_w"])
+            layer.norm_s.bias.data.copy_(w["norm_s_b"])
+        layer.proj_z[0].weight.data.copy_(w["norm_z_w"])
+        layer.proj_z[0].bias.data.copy_(w["norm_z_b"])
+        layer = layer.to(dtype)
+        set_linear(layer.in_proj, w["w_in"].to(dtype), w["b_in"].to(dtype))
+        set_linear(layer.proj_z[1], w["w_z"].to(dtype), None)
+        set_linear(layer.proj_o, w["w_o"].to(dtype), w["b_o"].to(dtype) if out_bias else None)
+        layer._ln_proj_moveaxis_pad = EagerPairBias()
+        return layer
+
+    # The weights (2.5 M values) are not stored: both this script and the tests rebuild them from the seeded recipes
+    # in oracle/triangle_oracle.py; the fixture keeps a checksum of every tensor to detect a change of generator.
+    sys.path.insert(0, str(HERE.parent.parent))
+    from oracle import triangle_oracle as orc
+
+    def checksum(weights) -> float:
+        return float(sum(t.double().abs().sum() for t in weights.__dict__.values() if t is not None))
+
+    g = torch.Generator().manual_seed(77)
+    out = {}
+    for case, (B, N, valid, initial_norm, out_bias, seed) in {"a": (1, 40, (33,), True, False, 501),
+                                                               "b": (2, 24, (24, 17), False, True, 502)}.items():
+        # weights, activations and mask rounded to bf16 so that the bf16 run and the kernels see the same numbers
+        wo = orc.make_pair_bias_attention_weights(seed, initial_norm=initial_norm, out_bias=out_bias).to(torch.bfloat16).to(torch.float32)
+        w = dict(wo.__dict__)
+        s = torch.randn(B, N, 384, generator=g).bfloat16().float()
+        z = torch.randn(B, N, N, 128, generator=g).bfloat16().float()
+        mask = torch.zeros(B, N)
+        for b, n_valid in enumerate(valid):
+            mask[b, :n_valid] = 1
+        upd32 = build(torch.float32, w, initial_norm, out_bias)(s, z, mask)
+        upd16 = build(torch.bfloat16, w, initial_norm, out_bias)(s.bfloat16(), z.bfloat16(), mask)
+        out.update({f"{case}_s": s, f"{case}_z": z, f"{case}_mask": mask, f"{case}_update": upd32,
+                    f"{case}_update_bf16": upd16, f"{case}_initial_norm": int(initial_norm),
+                    f"{case}_out_bias": int(out_bias), f"{case}_seed": seed, f"{case}_checksum": checksum(wo)})
+
+    two = orc.make_transition_weights(503, c=384, hidden=1536, std=0.05, identity_ln=False).to(torch.bfloat16).to(torch.float32)
+    tw = {"ln_w": two.ln_w, "ln_b": two.ln_b, "w1": two.w1, "w2": two.w2}
+    x = torch.randn(1, 40, 384, generator=g).bfloat16().float()
+    for name, dtype in (("t_update", torch.float32), ("t_update_bf16", torch.bfloat16)):
+        layer = Transition(384, 1536, dtype=dtype, skip_create_weights=True)
+        layer.norm.weight.data.copy_(tw["ln_w"])
+        layer.norm.bias.data.copy_(tw["ln_b"])
+        layer = layer.to(dtype)
+        set_linear(layer.fused_fc2_fc1, tw["w1"].to(dtype), None)
+        set_linear(layer.fc3, tw["w2"].to(dtype), None)
+        layer._swiglu = lambda t: torch.nn.functional.silu(t[..., 1536:].float()).to(t.dtype) * t[..., :1536]
+        out[name] = layer._forward_impl(x.to(dtype), None)
+    save("single_track", t_x=x, t_seed=503, t_checksum=checksum(two), **out)
 
 
 def trimul_cases() -> None:

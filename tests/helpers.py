@@ -32,3 +32,22 @@ def golden_transition_weights(g: dict, dtype=torch.float32) -> orc.TransitionWei
 def golden_trimul_weights(g: dict, dtype=torch.float32) -> orc.TriMulWeights:
     return orc.TriMulWeights(g["w_ln_in_w"], g["w_ln_in_b"], g["w_w_p_in"], g["w_w_g_in"], g["w_ln_out_w"],
                              g["w_ln_out_b"], g["w_w_p_out"], g["w_w_g_out"]).to(dtype)
+
+
+def _checksum(weights) -> float:
+    return float(sum(t.double().abs().sum() for t in weights.__dict__.values() if t is not None))
+
+
+def golden_single_attention_weights(g: dict, case: str) -> orc.PairBiasAttentionWeights:
+    """The seeded weights of a single-track fixture case (bf16-rounded, as fp32), checked against its checksum."""
+    w = orc.make_pair_bias_attention_weights(int(g[f"{case}_seed"]), initial_norm=bool(g[f"{case}_initial_norm"]),
+                                             out_bias=bool(g[f"{case}_out_bias"])).to(torch.bfloat16).to(torch.float32)
+    assert abs(_checksum(w) - g[f"{case}_checksum"]) < 1e-6 * g[f"{case}_checksum"], "weight recipe changed"
+    return w
+
+
+def golden_single_transition_weights(g: dict) -> orc.TransitionWeights:
+    w = orc.make_transition_weights(int(g["t_seed"]), c=384, hidden=1536, std=0.05, identity_ln=False)
+    w = w.to(torch.bfloat16).to(torch.float32)
+    assert abs(_checksum(w) - g["t_checksum"]) < 1e-6 * g["t_checksum"], "weight recipe changed"
+    return w

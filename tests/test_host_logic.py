@@ -78,7 +78,10 @@ def test_state_dict_contract_of_the_transition():
     assert sorted(b200.Transition(128, 512, dtype=torch.bfloat16, normalize=False).state_dict()) == [
         "fc3.weight", "fused_fc2_fc1.weight"]
     with pytest.raises(ValueError):
-        b200.Transition(256, 1024)
+        b200.Transition(200, 800)  # widths must be multiples of 128
+    single = b200.Transition(384, 1536, dtype=torch.bfloat16)  # the single-track transition
+    assert {k: tuple(v.shape) for k, v in single.state_dict().items()} == {
+        "norm.weight": (384,), "norm.bias": (384,), "fused_fc2_fc1.weight": (3072, 384), "fc3.weight": (384, 1536)}
 
 
 def test_linear_fused_segment_loading():
@@ -206,3 +209,66 @@ def test_pair_track_stack_has_the_reference_submodule_names():
     assert layer.tri_attn_end.node_type == b200.TriangleAttentionNodeType.ENDING
     assert layer.no_update_s and not layer.no_update_z
     assert b200.PairformerNoSeqModule(num_blocks=0)(torch.zeros(1, 4, 4, 128), torch.ones(1, 4, 4)).shape == (1, 4, 4, 128)
+
+
+def test_single_track_attention_state_dict_and_refusals():
+    """AttentionPairBias as the pairformer builds it (bionemo_ir/_torch/layers/attention.py:445-626): the reference
+    module's parameter names, and a ValueError for the options of other models."""
+    layer = b200.AttentionPairBias(layer_idx=0, c_s=384, c_z=128, num_heads=16, dtype=torch.bfloat16, bias_proj=True,
+                                   initial_norm=True)
+    assert {k: tuple(v.shape) for k, v in layer.state_dict().items()} == {
+        "norm_s.weight": (384,), "norm_s.bias": (384,), "in_proj.weight": (1536, 384), "in_proj.bias": (1536,),
+        "proj_z.0.weight": (128,), "proj_z.0.bias": (128,), "proj_z.1.weight": (16, 128), "proj_o.weight": (384, 384)}
+    plain = b200.AttentionPairBias(0, 384, 128, 16, initial_norm=False, bias_proj=True, out_bias=True, pair_norm=False)
+    assert sorted(plain.state_dict()) == ["in_proj.bias", "in_proj.weight", "proj_o.bias", "proj_o.weight",
+                                          "proj_z.0.weight"]
+    for bad in (dict(bias_proj=False), dict(bias_proj=True, use_separate_layer_norm=True),
+                dict(bias_proj=True, use_qk_norm=True), dict(bias_proj=True, output_gate_dim=384),
+                dict(bias_proj=True, norm_type="rms_norm"), dict(bias_proj=True, mask_left_aligned=False),
+                dict(bias_proj=True, dtype=torch.float16)):
+        with pytest.raises(ValueError):
+            b200.AttentionPairBias(0, 384, 128, 16, **bad)
+    with pytest.raises(ValueError):
+        b200.AttentionPairBias(0, 384, 128, 8, bias_proj=True)  # 16 heads only
+    with pytest.raises(ValueError, match="CUDA"):
+        layer(torch.zeros(1, 8, 384), torch.zeros(1, 8, 8, 128), torch.ones(1, 8))
+    with pytest.raises(ValueError):
+        layer(torch.zeros(1, 8, 384), torch.zeros(1, 8, 8, 128), torch.ones(1, 8), single_embedding=torch.zeros(1, 8, 384))
+
+
+def test_layer_norm_fold_for_the_tensor_core_gemm():
+    """fold_linear: LN(x) . W^T + b == rstd * (x . w_bf16^T) + nmr * rowsum + const, up to the bf16 rounding of W."""
+    from bionemo_inference_runtime_b200.layers.attention_pair_bias import fold_linear
+
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(37, 384, generator=g) * 2 + 0.7
+    w, b = torch.randn(96, 384, generator=g) * 0.05, torch.randn(96, generator=g)
+    gamma, beta = 1 + 0.2 * torch.randn(384, generator=g), 0.2 * torch.randn(384, generator=g)
+    wq, sc = fold_linear(w, b, gamma, beta)
+    assert wq.dtype == torch.bfloat16 and tuple(sc.shape) == (96, 2)
+    mean, var = x.mean(-1, keepdim=True), x.var(-1, unbiased=False, keepdim=True)
+    rstd = torch.rsqrt(var + 1e-5)
+    got = rstd * (x @ wq.float().T) + (-mean * rstd) * sc[:, 0] + sc[:, 1]
+    want = torch.nn.functional.linear(torch.nn.functional.layer_norm(x, (384,), gamma, beta), w, b)
+    torch.testing.assert_close(got, want, rtol=0, atol=2e-2)
+    wq2, sc2 = fold_linear(w, None, None, None)
+    assert torch.equal(wq2, w.bfloat16()) and not sc2.any()
+
+
+def test_pairformer_with_single_track_has_the_reference_submodule_names():
+    """PairformerLayerV1 / PairformerModule (bionemo_ir/_torch/layers/transformers/pairformer.py:44-252, 418-510)."""
+    class Config:
+        version, num_blocks, token_s, token_z, num_heads = "v1", 2, 384, 128, 16
+        torch_dtype, trimul_high_precision, attention_initial_norm, no_update_s = torch.bfloat16, False, True, False
+
+    stack = b200.PairformerModule(Config())
+    keys = set(stack.state_dict())
+    for sub in ("attention.norm_s.weight", "attention.in_proj.bias", "attention.proj_z.1.weight",
+                "attention.proj_o.weight", "transition_s.fused_fc2_fc1.weight", "transition_s.fc3.weight",
+                "tri_mul_out.p_in.weight", "tri_attn_end.pair_bias_proj.weight", "transition_z.fc3.weight"):
+        assert f"layers.1.{sub}" in keys
+    assert tuple(stack.layers[0].transition_s.fc3.weight.shape) == (384, 1536)
+    no_seq = b200.PairformerModule(num_blocks=1, no_update_s=True, dtype=torch.bfloat16)
+    assert not any(k.startswith("layers.0.attention") or "transition_s" in k for k in no_seq.state_dict())
+    with pytest.raises(ValueError):
+        b200.PairformerModule(num_blocks=1, no_update_z=True)

@@ -99,3 +99,28 @@ def test_triangle_multiplication_bf16_matches_the_unfused_reference_ops(name, di
     want = g[f"update_{name}_bf16{'_meannorm' if mean_norm else ''}"]
     # same ops in the same order; einsum summation order may differ by an ulp of the bf16 contraction result
     assert (upd.float() - want).abs().max() <= 2 ** -7 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("case", ["a", "b"])
+def test_single_track_attention_matches_the_reference_module(case):
+    """AttentionPairBias as the pairformer builds it: with and without initial norm / output bias, one and two
+    batch entries with different key counts."""
+    from tests.helpers import golden_single_attention_weights
+
+    g = load_golden("single_track")
+    w = golden_single_attention_weights(g, case)
+    got = orc.pair_bias_attention_forward(g[f"{case}_s"], g[f"{case}_z"], g[f"{case}_mask"], w)
+    torch.testing.assert_close(got, g[f"{case}_update"], rtol=1e-4, atol=1e-5)
+    got16 = orc.pair_bias_attention_forward(g[f"{case}_s"].bfloat16(), g[f"{case}_z"].bfloat16(), g[f"{case}_mask"],
+                                            w.to(torch.bfloat16))
+    torch.testing.assert_close(got16.float(), g[f"{case}_update_bf16"], rtol=2e-2, atol=2e-2)
+
+
+def test_single_track_transition_matches_the_reference_module():
+    from tests.helpers import golden_single_transition_weights
+
+    g = load_golden("single_track")
+    w = golden_single_transition_weights(g)
+    torch.testing.assert_close(orc.transition_forward(g["t_x"], None, w), g["t_update"], rtol=1e-4, atol=1e-5)
+    got16 = orc.transition_forward(g["t_x"].bfloat16(), None, w.to(torch.bfloat16))
+    torch.testing.assert_close(got16.float(), g["t_update_bf16"], rtol=2e-2, atol=4e-2)
