@@ -62,7 +62,7 @@ def test_pair_bias_pass_matches_layer_norm_projection_and_padding(B, Q, K, heads
 def test_dense_layer_kernel_row_and_swiglu_forms(rows, K, N):
     g = torch.Generator().manual_seed(rows)
     x = (torch.randn(2, rows, K, generator=g) + 0.3).bfloat16().to(DEV)
-    w, b = (torch.randn(N, K, generator=g) * 0.05).to(DEV), torch.randn(N, generator=g).to(DEV)
+    w, b = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(DEV), torch.randn(N, generator=g).to(DEV)
     gamma, beta = (1 + 0.2 * torch.randn(K, generator=g)).to(DEV), (0.2 * torch.randn(K, generator=g)).to(DEV)
     res = torch.randn(2, rows, N, generator=g).bfloat16().to(DEV)
     # plain projection with bias and residual
