@@ -48,11 +48,16 @@ WORKLOADS = {
                      desc="pair track of a 48-block Pairformer trunk (PairformerNoSeqModule: per block triangle "
                           "multiplication out + in, start+end TriangleAttention, transition), z[1,768,768,128] bf16, "
                           "all valid (pair track of BASELINE config 4), replayed from one CUDA graph"),
+    "cfg4": dict(B=1, N=768, valid="768", transition=True, trimul=True, blocks=48, single=True,
+                 desc="48-block Pairformer trunk (PairformerModule: per block triangle multiplication out + in, "
+                      "start+end TriangleAttention, pair transition, single-track attention with pair bias (c_s=384, "
+                      "16 heads), single transition), z[1,768,768,128] and s[1,768,384] bf16, all valid (BASELINE "
+                      "config 4), replayed from one CUDA graph"),
     "cfg5": dict(B=1, N=4096, valid="3900", transition=True, sharded=True, blocks=4,
                  desc="4 x (start node, all-to-all, end node, transition), z[1,4096,4096,128] bf16 row-sharded over the "
                       "GPUs, 3900 valid tokens (BASELINE config 5)"),
 }
-DEFAULT_STEPS = {"cfg2": 100, "cfg3": 20, "n768": 50, "block768": 50, "cfg4pair": 5, "cfg5": 3}
+DEFAULT_STEPS = {"cfg2": 100, "cfg3": 20, "n768": 50, "block768": 50, "cfg4pair": 5, "cfg4": 5, "cfg5": 3}
 
 
 def valid_lengths(spec: str, B: int, N: int, gen: torch.Generator) -> list[int]:
@@ -79,6 +84,13 @@ def trimul_flops(L: int, N: int) -> float:
     """One triangle-multiplication node: projections (128 -> 2x256, 2x 128 -> 128) on the L² valid positions plus the
     contraction, 2·L flops per valid position and channel (128 channels)."""
     return float(L) * L * (131072.0 + 65536.0 + 256.0 * L)
+
+
+def single_track_flops(L: int) -> float:
+    """Single track of one block for L valid tokens: in-projection (384 -> 4x384), pair-bias projection (128 -> 16 on
+    L² positions), q·k and p·v (16 heads of 24), output projection, and the transition (384 -> 2x1536 -> 384)."""
+    return float(L) * (2.0 * 384 * 1536 + 2.0 * 384 * 384 + 2.0 * 384 * 3072 + 2.0 * 1536 * 384) \
+        + float(L) * L * (2.0 * 128 * 16 + 4.0 * 16 * 24)
 
 
 def measured_peaks() -> tuple[float, float, str]:
@@ -232,8 +244,10 @@ def run_ours(args) -> dict:
     stack = None
     if cfg.get("blocks") and not cfg.get("sharded"):
         # a whole trunk: the package's stack module with random weights per block, one CUDA graph for all blocks
-        stack = b200.PairformerNoSeqModule(num_blocks=cfg["blocks"], dtype=torch.bfloat16, triangle_attn_backend="Heuristic",
-                                           trimul_high_precision=False, use_cuda_graph=True).to(device)
+        cls = b200.PairformerModule if cfg.get("single") else b200.PairformerNoSeqModule
+        extra = dict(attention_initial_norm=True) if cfg.get("single") else {}
+        stack = cls(num_blocks=cfg["blocks"], dtype=torch.bfloat16, triangle_attn_backend="Heuristic",
+                    trimul_high_precision=False, use_cuda_graph=True, **extra).to(device)
         gen = torch.Generator(device=device).manual_seed(2000 + rank)
         for name, prm in stack.named_parameters():
             if prm.dim() == 2:
@@ -241,7 +255,18 @@ def run_ours(args) -> dict:
             else:
                 prm.data.fill_(0.0 if name.endswith("bias") else 1.0)
 
-    def step(z, b=None):
+    single = bool(cfg.get("single"))
+    if single:
+        s_pin = torch.randn(cfg["B"], cfg["N"], 384, generator=torch.Generator().manual_seed(3000 + rank)).bfloat16().pin_memory()
+        s_out_pin = torch.empty_like(s_pin).pin_memory()
+        s_dev = s_pin.to(device)
+        token_mask = torch.stack([(torch.arange(cfg["N"]) < L).float() for L in lens]).to(device)
+    last_s = [None]
+
+    def step(z, b=None, s=None):
+        if stack is not None and single:
+            last_s[0], z_new = stack(s_dev if s is None else s, z, token_mask, mask_dev)
+            return z_new
         if stack is not None:
             return stack(z, mask_dev)
         b = bufs if b is None else b
@@ -253,9 +278,9 @@ def run_ours(args) -> dict:
             z2 = trans(z2, residual=True, inplace=True)
         return z2
 
-    launches_per_step = 6 + (1 if cfg["transition"] else 0) + 3 * len(trimul)
+    launches_per_step = 6 + (1 if cfg["transition"] else 0) + 3 * len(trimul) + (8 if single else 0)
     flops_step = sum(2 * node_flops(L) + (transition_flops(L) if cfg["transition"] else 0.0)
-                     + len(trimul) * trimul_flops(L, cfg["N"]) for L in lens)
+                     + len(trimul) * trimul_flops(L, cfg["N"]) + (single_track_flops(L) if single else 0.0) for L in lens)
     if stack is not None:
         launches_per_step *= cfg["blocks"]
         flops_step *= cfg["blocks"]
@@ -315,6 +340,10 @@ def run_ours(args) -> dict:
     slot_bufs: list[dict] = [{}, {}]
 
     def slot_step(zd, slot):
+        if single:  # the single representation travels with its pair tensor: in before the step, out after it
+            z_out = step(zd, slot_bufs[slot], s=s_pin.to(device, non_blocking=True))
+            s_out_pin.copy_(last_s[0], non_blocking=True)
+            return z_out
         return step(zd, slot_bufs[slot])
 
     pipe = b200.HostPipeline(slot_step, z_pin, device, depth=2)
@@ -363,7 +392,7 @@ def run_ours(args) -> dict:
         dist.all_reduce(total_flops, op=dist.ReduceOp.SUM)
     ms, e2e_ms, attn_ms = stats.tolist()
     flops_all = total_flops.item()
-    bytes_io = z_host.numel() * 2
+    bytes_io = z_host.numel() * 2 + (s_pin.numel() * 2 if single else 0)
 
     result = {
         "metric": "tri_attn_tflops", "value": flops_all / ms / 1e9, "unit": "TFLOP/s", "n_gpus": world,

@@ -145,8 +145,14 @@ class PairformerModule(nn.Module):
                       "trimul_mean_normalization": "trimul_mean_normalization", "s_path_dtype": "s_path_dtype",
                       "tri_attn_transposed_bias": "tri_attn_transposed_bias"}
 
-    def __init__(self, config=None, **kwargs):
+    def __init__(self, config=None, use_cuda_graph: bool = False, **kwargs):
+        """``use_cuda_graph`` (not in the reference, whose graph capture lives in its runtime) records one forward
+        of the whole stack per input shape and replays it; inputs are copied into the graph's buffers."""
         super().__init__()
+        self.use_cuda_graph = use_cuda_graph
+        self._graph = None
+        self._graph_key = None
+        self._graph_io = None
         if config is not None:
             if getattr(config, "version", "v1") != "v1":
                 raise ValueError("only the v1 pairformer layer is built on the sm_100a kernels")
@@ -163,6 +169,29 @@ class PairformerModule(nn.Module):
                 buffers: PreallocatedBuffers | None = None, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
         if not self.layers:
             return s, z
+        if not (self.use_cuda_graph and z.is_cuda) or torch.cuda.is_current_stream_capturing():
+            return self._run(s, z, mask, pair_mask, attn_metadatas, buffers, **kwargs)
+        inputs = (s, z, mask, pair_mask)
+        key = tuple((tuple(t.shape), t.dtype, t.device) for t in inputs)
+        if self._graph is None or key != self._graph_key:
+            static = [t.clone() for t in inputs]
+            graph_buffers: dict = {}
+            side = torch.cuda.Stream(z.device)
+            side.wait_stream(torch.cuda.current_stream(z.device))
+            with torch.cuda.stream(side):
+                self._run(*static, attn_metadatas, graph_buffers, **kwargs)  # warm-up: folds the weights
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    outs = self._run(*static, attn_metadatas, graph_buffers, **kwargs)
+            torch.cuda.current_stream(z.device).wait_stream(side)
+            self._graph, self._graph_key, self._graph_io = graph, key, (static, outs, graph_buffers)
+        static, outs, _ = self._graph_io
+        for dst, src in zip(static, inputs):
+            dst.copy_(src)
+        self._graph.replay()
+        return outs[0].clone(), outs[1].clone()
+
+    def _run(self, s, z, mask, pair_mask, attn_metadatas, buffers, **kwargs):
         first = self.layers[0]
         precomputed = precompute_pair_masks(first.triangle_attn_backend, pair_mask, inf=first.tri_attn_start.inf,
                                             dtype=first.dtype)

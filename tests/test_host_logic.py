@@ -272,3 +272,24 @@ def test_pairformer_with_single_track_has_the_reference_submodule_names():
     assert not any(k.startswith("layers.0.attention") or "transition_s" in k for k in no_seq.state_dict())
     with pytest.raises(ValueError):
         b200.PairformerModule(num_blocks=1, no_update_z=True)
+
+
+def test_boltz_single_track_attention_converter_feeds_a_strict_load():
+    """Boltz checkpoint names (proj_q with bias, proj_g / proj_k / proj_v without) -> in_proj in q, gate, k, v order
+    (bionemo_ir/models/boltz1/convert.py:64-98)."""
+    from bionemo_inference_runtime_b200.convert_utils import get_attention_pair_bias_weights
+
+    g = torch.Generator().manual_seed(4)
+    ckpt = {f"m.attention.proj_{n}.weight": torch.randn(384, 384, generator=g) for n in "qkvg"}
+    ckpt.update({"m.attention.proj_q.bias": torch.randn(384, generator=g), "m.attention.norm_s.weight": torch.ones(384),
+                 "m.attention.norm_s.bias": torch.zeros(384), "m.attention.proj_z.0.weight": torch.ones(128),
+                 "m.attention.proj_z.0.bias": torch.zeros(128), "m.attention.proj_z.1.weight": torch.randn(16, 128, generator=g),
+                 "m.attention.proj_o.weight": torch.randn(384, 384, generator=g)})
+    sd = get_attention_pair_bias_weights(ckpt, "m.attention", "attention", dtype="bfloat16")
+    layer = b200.AttentionPairBias(0, 384, 128, 16, dtype=torch.bfloat16, bias_proj=True, initial_norm=True)
+    layer.load_state_dict({k.removeprefix("attention."): v for k, v in sd.items()}, strict=True)
+    w = layer.in_proj.weight
+    assert torch.equal(w[384:768].cpu(), ckpt["m.attention.proj_g.weight"].bfloat16())
+    assert torch.equal(w[768:1152].cpu(), ckpt["m.attention.proj_k.weight"].bfloat16())
+    assert torch.equal(layer.in_proj.bias[:384].cpu(), ckpt["m.attention.proj_q.bias"].bfloat16())
+    assert not layer.in_proj.bias[384:].any()
