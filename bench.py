@@ -231,7 +231,10 @@ def run_ours(args) -> dict:
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    cfg = WORKLOADS[args.workload]
+    cfg = dict(WORKLOADS[args.workload])
+    if args.blocks is not None and cfg.get("blocks") and not cfg.get("sharded"):
+        cfg["blocks"] = args.blocks
+        cfg["desc"] += f" [--blocks {args.blocks}]"
     z_host, mask_host, lens, w_start, w_end, w_tr = make_inputs(cfg, 1000 + rank, device)
     start, end, trans = build_modules(w_start, w_end, w_tr, device)
     pre = b200.precompute_pair_masks("Heuristic", mask_host.to(device))
@@ -647,6 +650,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
+    ap.add_argument("--blocks", type=int, default=None,
+                    help="override the number of blocks of a stack workload (cfg4, cfg4pair), e.g. 1 for a profile")
     ap.add_argument("--exchange", choices=["all_to_all", "peer_stores"], default="peer_stores",
                     help="sharded workloads: how the rows->columns transpose crosses the links (NCCL all-to-all, or "
                          "stores from the starting node's output kernel into the peers' column shards)")

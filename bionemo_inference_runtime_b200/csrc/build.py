@@ -20,7 +20,7 @@ PKG = CSRC.parent
 LIB = PKG / "libb200ta.so"
 OBJ_DIR = CSRC / "build"
 SOURCES = ["host.cu", "pack.cu", "rowgemm.cu", "attention.cu", "node.cu", "transition.cu", "trimul_project.cu",
-           "trimul_contract.cu", "trimul_output.cu", "linear.cu"]
+           "trimul_contract.cu", "trimul_output.cu", "linear.cu", "pair_bias.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--use_fast_math",

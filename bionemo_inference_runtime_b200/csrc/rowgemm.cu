@@ -36,7 +36,6 @@ struct RowGemmParams {
   float eps;
   __nv_bfloat16* bias;
   long long bs_b, bs_h, bs_q, bs_k;
-  int bias_heads;  // bias columns written: 4 (triangle bias) or up to 16 (pair bias of the single track)
   __nv_bfloat16* out;                         // prologue: q/k/v/g planes; epilogue: output pair tensor
   long long qs_which, qs_br, qs_h, qs_s;      // prologue strides (elements)
   long long os_b, os_r, os_s;                 // epilogue strides (elements)
@@ -256,7 +255,7 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         tc_fence_after();
         const uint32_t acc_addr = lane_taddr + slot * kSlotCols;
         if (MODE == kPrologue && u == 2) {
-          // bias heads: columns 512..512+bias_heads of the folded projection (first warpgroup only)
+          // triangle-bias heads: columns 512..515 of the folded projection (first warpgroup only)
           if (e == 0) {
             uint32_t a[16];
             tmem_ld16(acc_addr, a);
@@ -264,8 +263,7 @@ rowgemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const float4* sc4 = reinterpret_cast<const float4*>(gen + L::kVec) + 256;
             if (p.bias != nullptr && s < p.S_pad) {
 #pragma unroll
-              for (int hp = 0; hp < 8; ++hp) {
-                if (2 * hp >= p.bias_heads) break;
+              for (int hp = 0; hp < 2; ++hp) {
                 const float4 t = sc4[hp];  // {rowsum0, rowsum1, const0, const1}
                 const float v0 = s < p.S ? fmaf(rstd, __uint_as_float(a[2 * hp]), fmaf(nmr, t.x, t.z)) : 0.f;
                 const float v1 = s < p.S ? fmaf(rstd, __uint_as_float(a[2 * hp + 1]), fmaf(nmr, t.y, t.w)) : 0.f;
@@ -446,13 +444,13 @@ int launch_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, co
 }  // namespace
 }  // namespace b200ta
 
-namespace b200ta {
-namespace {
+extern "C" {
 
-int launch_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, const void* packed, float eps,
+int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, const void* packed, float eps,
                     void* qkvg, int64_t qs_which, int64_t qs_br, int64_t qs_h, int64_t qs_s, int want_qkvg,
-                    void* bias, int64_t bs_b, int64_t bs_h, int64_t bs_q, int64_t bs_k, int bias_heads, int B, int R,
-                    int S, int S_pad, void* stream) {
+                    void* bias, int64_t bs_b, int64_t bs_h, int64_t bs_q, int64_t bs_k, int B, int R, int S,
+                    int S_pad, void* stream) {
+  using namespace b200ta;
   B200TA_REQUIRE(z && packed, "prologue: NULL pointer");
   B200TA_REQUIRE(B > 0 && R > 0 && S > 0 && S_pad >= S, "prologue: bad sizes B=%d R=%d S=%d S_pad=%d", B, R, S, S_pad);
   B200TA_REQUIRE(want_qkvg ? qkvg != nullptr : bias != nullptr, "prologue: nothing to write");
@@ -491,7 +489,6 @@ int launch_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
   p.eps = eps;
   p.bias = static_cast<__nv_bfloat16*>(bias);
   p.bs_b = bs_b, p.bs_h = bs_h, p.bs_q = bs_q, p.bs_k = bs_k;
-  p.bias_heads = bias_heads;
   p.out = static_cast<__nv_bfloat16*>(qkvg);
   p.qs_which = qs_which, p.qs_br = qs_br, p.qs_h = qs_h, p.qs_s = qs_s;
   p.want_qkvg = want_qkvg ? 1 : 0;
@@ -505,30 +502,6 @@ int launch_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
   kern<<<grid, kThreads, Smem<kPrologue>::kDynamic, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_w, tm_a, p);
   B200TA_CHECK_CUDA(cudaGetLastError());
   return B200TA_OK;
-}
-
-}  // namespace
-}  // namespace b200ta
-
-extern "C" {
-
-int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, const void* packed, float eps,
-                    void* qkvg, int64_t qs_which, int64_t qs_br, int64_t qs_h, int64_t qs_s, int want_qkvg,
-                    void* bias, int64_t bs_b, int64_t bs_h, int64_t bs_q, int64_t bs_k, int B, int R, int S,
-                    int S_pad, void* stream) {
-  return b200ta::launch_prologue(z, zs_b, zs_r, zs_s, packed, eps, qkvg, qs_which, qs_br, qs_h, qs_s, want_qkvg, bias,
-                                 bs_b, bs_h, bs_q, bs_k, b200ta::kHeads, B, R, S, S_pad, stream);
-}
-
-int b200ta_pair_bias(const void* z, int64_t zs_b, int64_t zs_q, int64_t zs_k, const void* packed, float eps,
-                     void* bias, int64_t bs_b, int64_t bs_h, int64_t bs_q, int64_t bs_k, int num_heads, int B, int Q,
-                     int K, int K_pad, void* stream) {
-  using namespace b200ta;
-  B200TA_REQUIRE(bias, "pair_bias: NULL pointer");
-  B200TA_REQUIRE(num_heads > 0 && num_heads <= 16 && num_heads % 2 == 0,
-                 "pair_bias: num_heads=%d must be even and at most 16", num_heads);
-  return b200ta::launch_prologue(z, zs_b, zs_q, zs_k, packed, eps, nullptr, 0, 0, 0, 0, 0, bias, bs_b, bs_h, bs_q,
-                                 bs_k, num_heads, B, Q, K, K_pad, stream);
 }
 
 int b200ta_epilogue(const void* og, int64_t gs_b, int64_t gs_r, int64_t gs_s, const void* packed,
