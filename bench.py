@@ -387,6 +387,51 @@ def run_ours(args) -> dict:
     attn_flops = sum(attention_core_flops(L) for L in lens)
     peak_tf, peak_gbs, peak_kind = measured_peaks()
 
+    # ---- the single track's kernels one by one (CUDA events, L2 flushed before each launch) -----------------------
+    single_kernels = None
+    if single:
+        import math
+
+        layer = stack.layers[0]
+        att, tr_s = layer.attention, layer.transition_s
+        wts = att._weights(device)
+        stats = ops.row_stats(s_dev)
+        planes = ops.linear(s_dev, wts["w_in"], wts["sc_in"], ops.LINEAR_PLANES, B=B, rows=N, stats=stats)
+        pbias = att.project_pair_bias(z_dev)
+        len4 = torch.tensor(lens, dtype=torch.int32, device=device).repeat_interleave(4)
+        q4, b4 = planes.view(4, 4 * B, 4, N, 32), pbias.view(4 * B, 4, N, pbias.shape[-1])
+        o4 = ops.attention(q4, b4, len4, 4 * B, 1, N, scale=1 / math.sqrt(24))
+
+        def event_us(fn):
+            ts = []
+            for i in range(13):
+                flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                e1.synchronize()
+                if i >= 3:
+                    ts.append(e0.elapsed_time(e1) * 1e3)
+            return sorted(ts)[len(ts) // 2]
+
+        pair_bias_us = event_us(lambda: att.project_pair_bias(z_dev, bias=pbias))
+        pair_bias_bytes = z_dev.numel() * 2 + pbias.numel() * 2
+        single_kernels = {
+            "unit": "us per launch, median of 10",
+            "row_stats": event_us(lambda: ops.row_stats(s_dev, stats=stats)),
+            "linear_in_proj": event_us(lambda: ops.linear(s_dev, wts["w_in"], wts["sc_in"], ops.LINEAR_PLANES, B=B, rows=N,
+                                                          stats=stats, out=planes)),
+            "pair_bias": pair_bias_us,
+            "pair_bias_roofline": {"bound": "hbm", "achieved": pair_bias_bytes / pair_bias_us / 1e3, "peak": peak_gbs,
+                                   "unit": "GB/s", "frac": pair_bias_bytes / pair_bias_us / 1e3 / peak_gbs,
+                                   "algorithmic_bytes": pair_bias_bytes},
+            "attention_16_heads": event_us(lambda: ops.attention(q4, b4, len4, 4 * B, 1, N, out=o4, scale=1 / math.sqrt(24))),
+            "linear_out_proj": event_us(lambda: ops.linear(o4, wts["w_o"], wts["sc_o"], ops.LINEAR_ROWS, B=B, rows=N,
+                                                           a_strides=(4 * N * 128, 128, N * 128), residual=s_dev)),
+            "transition_s_3_launches": event_us(lambda: tr_s(s_dev, residual=True)),
+        }
+
     # ---- aggregate over ranks ------------------------------------------------------------------------------
     stats = torch.tensor([ms, e2e_ms, attn_ms], dtype=torch.float64, device=device)
     total_flops = torch.tensor([flops_step], dtype=torch.float64, device=device)
@@ -415,6 +460,8 @@ def run_ours(args) -> dict:
                      "peak_source": f"{peak_kind} bf16 burst", "ms_per_launch": attn_ms, "traffic": TRAFFIC.get(args.workload)},
         "clocks": clocks.summary(),
     }
+    if single_kernels is not None:
+        result["single_track_kernels"] = single_kernels
     if rank == 0 and world == 1 and not args.no_cpu_baseline and not cfg.get("trimul"):  # the CPU sample covers rows of the attention nodes and the transition only
         result["cpu_baseline"] = cpu_baseline(cfg, args.workload)
     if world > 1:
