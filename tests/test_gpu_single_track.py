@@ -204,3 +204,31 @@ def test_pairformer_layer_with_single_track_matches_the_oracle():
     # triangle multiplication, and padded queries of s read them through the pair bias
     torch.testing.assert_close(got_z.float().cpu()[:, :valid, :valid], want_z[:, :valid, :valid], rtol=3e-2, atol=6e-2)
     torch.testing.assert_close(got_s.float().cpu()[:, :valid], want_s[:, :valid], rtol=3e-2, atol=6e-2)
+
+
+def test_pairformer_module_graph_replay_matches_eager():
+    torch.manual_seed(5)
+    N = 64
+    kw = dict(num_blocks=2, dtype=torch.bfloat16, trimul_high_precision=False, attention_initial_norm=True)
+    eager = b200.PairformerModule(**kw).to(DEV)
+    gen = torch.Generator(device=DEV).manual_seed(11)
+    for name, prm in eager.named_parameters():
+        if prm.dim() == 2:
+            prm.data.copy_(torch.randn(prm.shape, generator=gen, device=DEV) * 0.03)
+        else:
+            prm.data.fill_(0.0 if name.endswith("bias") else 1.0)
+    graphed = b200.PairformerModule(use_cuda_graph=True, **kw).to(DEV)
+    graphed.load_state_dict(eager.state_dict(), strict=True)
+    m = (torch.arange(N, device=DEV) < 57).float()[None]
+    pair_mask = m[:, :, None] * m[:, None, :]
+    outs = []
+    for seed in (1, 2):
+        g = torch.Generator(device=DEV).manual_seed(seed)
+        s = torch.randn(1, N, 384, generator=g, device=DEV).bfloat16()
+        z = torch.randn(1, N, N, 128, generator=g, device=DEV).bfloat16()
+        want_s, want_z = eager(s.clone(), z.clone(), m, pair_mask)
+        got_s, got_z = graphed(s, z, m, pair_mask)  # first call records, second replays
+        _ok()
+        assert torch.equal(got_s, want_s) and torch.equal(got_z, want_z)
+        outs.append(got_s)
+    assert not torch.equal(outs[0], outs[1])
