@@ -68,20 +68,29 @@ class KernelStages:
     def transition(self, layer, x: torch.Tensor) -> torch.Tensor:
         return layer(x, residual=True, inplace=True)
 
-    def epilogue_scatter(self, node, og, residual_kernel_order, peer_ptrs: list[int], rank: int):
+    def peer_shard(self, shape, device, group) -> "_PeerShard":
+        """A bf16 shard buffer of this rank that the other ranks' kernels can store into."""
+        return _PeerShard(shape, device, group)
+
+    def transition_scatter_ok(self, cols_per_rank: int) -> bool:
+        return cols_per_rank % 32 == 0  # the transition's TMA stores move 32 rows at a time
+
+    def epilogue_scatter(self, node, og, residual_kernel_order, cols_shard: "_PeerShard", rank: int):
         """o_proj + residual of the ROWS shard, written transposed into every GPU's COLS shard (peer stores)."""
         B, R, S, _ = og.shape
         packed = node._packed(og.device)
         r = residual_kernel_order
+        peer_ptrs = cols_shard.ptrs
         ptrs = (ctypes.c_void_p * len(peer_ptrs))(*peer_ptrs)
         _lib.call("b200ta_epilogue_scatter", og.data_ptr(), og.stride(0), og.stride(1), og.stride(2), packed.data_ptr(),
                   r.data_ptr(), *r.stride()[:3], ptrs, len(peer_ptrs), rank, B, R, S,
                   torch.cuda.current_stream().cuda_stream)
 
 
-    def transition_scatter(self, layer, x_cols, peer_ptrs: list[int], rank: int):
+    def transition_scatter(self, layer, x_cols, rows_shard: "_PeerShard", rank: int):
         """The transition (+ residual) of the COLS shard, written into every GPU's ROWS shard (peer TMA stores)."""
         B, N, n, _ = x_cols.shape
+        peer_ptrs = rows_shard.ptrs
         ptrs = (ctypes.c_void_p * len(peer_ptrs))(*peer_ptrs)
         eps = layer.eps if layer.norm is None else layer.norm.eps
         _lib.call("b200ta_transition_scatter", x_cols.data_ptr(), None, layer._packed(x_cols.device).data_ptr(), eps,
@@ -168,14 +177,14 @@ class ShardedPairBlock:
         world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         B, n, N, c = z_rows.shape
         if self._cols is None or self._cols.shape != (B, N, n, c):
-            self._cols = _PeerShard((B, N, n, c), z_rows.device, self.group)
+            self._cols = self.stages.peer_shard((B, N, n, c), z_rows.device, self.group)
         node = self.start_node
         qkvg, bias_local = self.stages.prologue(node, z_rows)
         bias_full = gather_bias(bias_local, self.group)
         og = self.stages.attention(node, qkvg, bias_full, lengths_rows, B, n, N)
         # The bias all-gather above already orders this call after every rank's last read of its column shard (the
         # exchange back to rows, or the caller's use of a ``keep_layout`` result, precedes its next call).
-        self.stages.epilogue_scatter(node, og, z_rows, self._cols.ptrs, rank)
+        self.stages.epilogue_scatter(node, og, z_rows, self._cols, rank)
         self._barrier(z_rows.device)  # every rank's stores into this rank's column shard have landed
         return self._cols.tensor
 
@@ -204,12 +213,13 @@ class ShardedPairBlock:
             z_cols = exchange(z_rows, COLS, self.group)
         z_cols = self._node(self.end_node, z_cols, COLS, lengths_cols)
         B, N, n, c = z_cols.shape
-        if self.fused_transpose and self.transition is not None and not keep_layout and n % 32 == 0:
+        if (self.fused_transpose and self.transition is not None and not keep_layout
+                and self.stages.transition_scatter_ok(n)):
             if self._rows is None or self._rows.shape != (B, n, N, c):
-                self._rows = _PeerShard((B, n, N, c), z_cols.device, self.group)
+                self._rows = self.stages.peer_shard((B, n, N, c), z_cols.device, self.group)
             # every rank has read its row shard of the previous call (prologue and residual of the starting node)
             # before the barrier that follows the starting node of this call
-            self.stages.transition_scatter(self.transition, z_cols, self._rows.ptrs, dist.get_rank(self.group))
+            self.stages.transition_scatter(self.transition, z_cols, self._rows, dist.get_rank(self.group))
             self._barrier(z_cols.device)  # every rank's stores into this rank's row shard have landed
             return self._rows.tensor
         if self.transition is not None:

@@ -43,6 +43,24 @@ class OracleStages:
         x.copy_(orc.transition_forward(x, None, w_t, residual=True))
         return x
 
+    # The fused-transpose stages: on CPU ranks the "peer stores" are an exchange into the local shard buffer, so
+    # the driver's ordering of stages and buffers is what gets tested.
+    class _Shard:
+        def __init__(self, shape):
+            self.tensor, self.shape, self.ptrs = torch.full(shape, float("nan")), tuple(shape), None
+
+    def peer_shard(self, shape, device, group):
+        return self._Shard(shape)
+
+    def transition_scatter_ok(self, cols_per_rank):
+        return True
+
+    def epilogue_scatter(self, w, og, residual, cols_shard, rank):
+        cols_shard.tensor.copy_(sharded.exchange(residual + F.linear(og, w.w_out, w.b_out), sharded.COLS))
+
+    def transition_scatter(self, w_t, x_cols, rows_shard, rank):
+        rows_shard.tensor.copy_(sharded.exchange(orc.transition_forward(x_cols, None, w_t, residual=True), sharded.ROWS))
+
 
 def _inputs():
     g = torch.Generator().manual_seed(7)
@@ -57,16 +75,18 @@ def _inputs():
     return z, mask, w1, w2, wt
 
 
-def _worker(rank: int, port: int, results):
+def _worker(rank: int, port: int, fused: bool, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=WORLD)
     try:
         z, mask, w1, w2, wt = _inputs()
-        block = sharded.ShardedPairBlock(w1, w2, wt, stages=OracleStages())
+        block = sharded.ShardedPairBlock(w1, w2, wt, stages=OracleStages(), fused_transpose=fused)
         z_rows = sharded.shard(z, rank, WORLD, sharded.ROWS)
         lengths_rows = orc.row_lengths(sharded.shard(mask.unsqueeze(-1), rank, WORLD, sharded.ROWS).squeeze(-1))
         lengths_cols = orc.row_lengths(sharded.shard(mask.unsqueeze(-1), rank, WORLD, sharded.COLS).squeeze(-1).transpose(1, 2))
         out_rows = block(z_rows.clone(), lengths_rows, lengths_cols)
+        if fused:  # a second call reuses the shard buffers
+            out_rows = block(z_rows.clone(), lengths_rows, lengths_cols).clone()
         # the exchange round trip must be the identity
         rt = sharded.exchange(sharded.exchange(z_rows.clone(), sharded.COLS), sharded.ROWS)
         gathered = [torch.empty_like(out_rows) for _ in range(WORLD)]
@@ -77,11 +97,12 @@ def _worker(rank: int, port: int, results):
         dist.destroy_process_group()
 
 
-def test_sharded_block_matches_unsharded_oracle():
+@pytest.mark.parametrize("fused", [False, True], ids=["all_to_all", "fused_transpose"])
+def test_sharded_block_matches_unsharded_oracle(fused):
     ctx = mp.get_context("spawn")
     results = ctx.Queue()
-    port = 29500 + os.getpid() % 2000
-    procs = [ctx.Process(target=_worker, args=(r, port, results)) for r in range(WORLD)]
+    port = 29500 + os.getpid() % 2000 + int(fused)
+    procs = [ctx.Process(target=_worker, args=(r, port, fused, results)) for r in range(WORLD)]
     for p in procs:
         p.start()
     got, roundtrip_ok = results.get(timeout=120)
