@@ -1,8 +1,9 @@
 """Module-level API: the reference's pair-track layers on the sm_100a kernels."""
 
 from .attention_backend import (AttentionBackend, AttentionMetadata, AttentionType, B200TriangleAttention,
-                                PrecomputedPairMasks, create_attention, get_attention_backend, mask_to_lengths,
-                                precompute_pair_masks, register_precompute_pair_masks)
+                                PrecomputedPairMasks, PrecomputedSingleMasks, create_attention, get_attention_backend,
+                                mask_to_lengths, precompute_pair_masks, precompute_single_masks,
+                                register_precompute_pair_masks, register_precompute_single_masks)
 from .attention_pair_bias import AttentionPairBias
 from .auto_chunk import (CHUNK_REGISTRY, PAIR_TRANSITION, TRIANGLE_ATTENTION, ChunkPolicy, chunk_apply,
                          default_autochunk_min, iter_chunks)
@@ -25,5 +26,6 @@ __all__ = [
     "TriangleAttentionNode", "TriangleAttentionNodeType", "TriangleAttentionStartingNode", "split_pair_bias_proj",
     "TriangleMultiplicationMetadata", "TriangleMultiplicationNode", "TriangleMultiplicationNodeType",
     "precompute_trimul_metadata", "set_trimul_token_padding", "PairformerNoSeqLayer", "PairformerNoSeqModule",
-    "AttentionPairBias", "PairformerLayerV1", "PairformerModule",
+    "AttentionPairBias", "PairformerLayerV1", "PairformerModule", "PrecomputedSingleMasks", "precompute_single_masks",
+    "register_precompute_single_masks",
 ]

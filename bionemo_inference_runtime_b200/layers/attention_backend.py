@@ -215,3 +215,59 @@ def _length_precompute(pair_mask, inf=1e9, dtype=None):
 
 for _name in TRIANGLE_BACKENDS:
     register_precompute_pair_masks(_name, _length_precompute if _name in _LENGTH_BACKENDS else _additive_precompute)
+
+
+# ---- single-track masks (AttentionPairBias) -----------------------------------------------------------------------
+
+
+@dataclass
+class PrecomputedSingleMasks:
+    """The single mask ``[*, I]`` in the form the attention consumes, computed once before the layer loop
+    (reference: ``PrecomputedSingleMasks``, bionemo_ir/_torch/attention_backend/utils.py:399-426)."""
+
+    single_mask: torch.Tensor
+    mask_bias: torch.Tensor
+    mask_bias_local: torch.Tensor | None = None
+    excluded: torch.Tensor | None = None
+    value_mask: torch.Tensor | None = None
+
+
+PrecomputeSingleMasksFn = Callable[[torch.Tensor, float], PrecomputedSingleMasks]
+_PRECOMPUTE_SINGLE_MASKS_REGISTRY: dict[str, PrecomputeSingleMasksFn] = {}
+
+
+def register_precompute_single_masks(backend_name: str, fn: PrecomputeSingleMasksFn) -> None:
+    _PRECOMPUTE_SINGLE_MASKS_REGISTRY[backend_name] = fn
+
+
+def precompute_single_masks(backend_name: str, single_mask: torch.Tensor, inf: float = 1e9, query_to_keys=None,
+                            activation_dtype: torch.dtype | None = None) -> PrecomputedSingleMasks:
+    """Same dispatch as the reference (utils.py:441-483).  ``query_to_keys`` (sequence-local attention) is not
+    supported by the sm_100a single track and raises."""
+    fn = _PRECOMPUTE_SINGLE_MASKS_REGISTRY.get(backend_name)
+    if fn is None:
+        raise ValueError(f"No precompute_single_masks registered for backend '{backend_name}'. "
+                         f"Available: {sorted(_PRECOMPUTE_SINGLE_MASKS_REGISTRY.keys())}")
+    if query_to_keys is not None:
+        raise ValueError("sequence-local attention (query_to_keys) is not supported by the sm_100a single track")
+    result = fn(single_mask, inf)
+    if activation_dtype is not None:
+        valid = single_mask.unsqueeze(-1)
+        result.excluded = ~valid.to(torch.bool)
+        result.value_mask = valid.to(activation_dtype)
+    return result
+
+
+def _additive_single(single_mask: torch.Tensor, inf: float = 1e9) -> PrecomputedSingleMasks:
+    return PrecomputedSingleMasks(single_mask, ((1 - single_mask.float()) * -inf)[..., None, None, :])
+
+
+def _length_single(single_mask: torch.Tensor, inf: float = 1e9) -> PrecomputedSingleMasks:
+    del inf
+    return PrecomputedSingleMasks(single_mask, (single_mask.float() > 0.5).sum(dim=-1, dtype=torch.int32).reshape(-1))
+
+
+for _name in ("VANILLA", "SDPA"):
+    register_precompute_single_masks(_name, _additive_single)
+for _name in ("CuTeDSL", "Heuristic"):
+    register_precompute_single_masks(_name, _length_single)

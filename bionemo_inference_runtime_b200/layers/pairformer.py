@@ -19,7 +19,8 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from .attention_backend import AttentionMetadata, PrecomputedPairMasks, precompute_pair_masks
+from .attention_backend import (AttentionMetadata, PrecomputedPairMasks, precompute_pair_masks,
+                                precompute_single_masks)
 from .attention_pair_bias import AttentionPairBias
 from .auto_chunk import CHUNK_REGISTRY, PAIR_TRANSITION
 from .buffers import PreallocatedBuffers
@@ -201,9 +202,12 @@ class PairformerModule(nn.Module):
         trimul_metadata = precompute_trimul_metadata(
             z, precomputed.mask_bias if int_lengths else None,
             precomputed.mask_bias_transposed if int_lengths else None, enabled=self.pair_mask_left_aligned)
+        # the key mask of the single track, reduced once for all layers (reference: pairformer.py:472-476)
+        precomputed_single = None if first.no_update_s else precompute_single_masks(
+            first.pairwise_attn_backend, mask, inf=first.attention.inf)
         for layer in self.layers:
             s, z = layer(s, z, mask, pair_mask, trimul_metadata, attn_metadatas, precomputed_masks=precomputed,
-                         buffers=buffers, **kwargs)
+                         precomputed_single_masks=precomputed_single, buffers=buffers, **kwargs)
         return s, z
 
 

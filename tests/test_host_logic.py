@@ -293,3 +293,24 @@ def test_boltz_single_track_attention_converter_feeds_a_strict_load():
     assert torch.equal(w[768:1152].cpu(), ckpt["m.attention.proj_k.weight"].bfloat16())
     assert torch.equal(layer.in_proj.bias[:384].cpu(), ckpt["m.attention.proj_q.bias"].bfloat16())
     assert not layer.in_proj.bias[384:].any()
+
+
+def test_single_mask_precompute_registry_and_key_counts():
+    """precompute_single_masks (bionemo_ir/_torch/attention_backend/utils.py:441-518): additive bias for the eager
+    backends, int32 key counts for the left-mask kernel; the attention layer reads the same count from each."""
+    mask = torch.tensor([[1., 1., 1., 0., 0.], [1., 1., 1., 1., 1.]])
+    add = b200.precompute_single_masks("VANILLA", mask, inf=1e9)
+    assert tuple(add.mask_bias.shape) == (2, 1, 1, 5) and add.mask_bias[0, 0, 0, 3] == -1e9 and add.mask_bias[1].abs().sum() == 0
+    cnt = b200.precompute_single_masks("CuTeDSL", mask, activation_dtype=torch.bfloat16)
+    assert cnt.mask_bias.dtype == torch.int32 and cnt.mask_bias.tolist() == [3, 5]
+    assert cnt.excluded.shape == (2, 5, 1) and cnt.value_mask.dtype == torch.bfloat16
+    with pytest.raises(ValueError):
+        b200.precompute_single_masks("no-such-backend", mask)
+    with pytest.raises(ValueError):
+        b200.precompute_single_masks("VANILLA", mask, query_to_keys=lambda t: t)
+    layer = b200.AttentionPairBias(0, 384, 128, 16, bias_proj=True)
+    dev = torch.device("cpu")
+    for form in (dict(mask=mask, mask_bias=None), dict(mask=mask, mask_bias=add.mask_bias),
+                 dict(mask=None, mask_bias=cnt.mask_bias)):
+        assert layer._lengths(form["mask"], form["mask_bias"], 2, 5, dev).tolist() == [3, 5]
+    assert layer._lengths(None, None, 2, 5, dev).tolist() == [5, 5]
