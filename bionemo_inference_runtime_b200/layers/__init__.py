@@ -9,7 +9,8 @@ from .auto_chunk import (CHUNK_REGISTRY, PAIR_TRANSITION, TRIANGLE_ATTENTION, Ch
                          default_autochunk_min, iter_chunks)
 from .buffers import PreallocatedBuffers, ensure_buffer
 from .linear import Linear, WeightMode, WeightsLoadingConfig
-from .pairformer import PairformerLayerV1, PairformerModule, PairformerNoSeqLayer, PairformerNoSeqModule
+from .pairformer import (PairformerLayerV1, PairformerLayerV2, PairformerModule, PairformerNoSeqLayer,
+                         PairformerNoSeqModule)
 from .transition import Transition
 from .triangle_multiplication import (TriangleMultiplicationMetadata, TriangleMultiplicationNode,
                                       TriangleMultiplicationNodeType, precompute_trimul_metadata,
@@ -26,6 +27,6 @@ __all__ = [
     "TriangleAttentionNode", "TriangleAttentionNodeType", "TriangleAttentionStartingNode", "split_pair_bias_proj",
     "TriangleMultiplicationMetadata", "TriangleMultiplicationNode", "TriangleMultiplicationNodeType",
     "precompute_trimul_metadata", "set_trimul_token_padding", "PairformerNoSeqLayer", "PairformerNoSeqModule",
-    "AttentionPairBias", "PairformerLayerV1", "PairformerModule", "PrecomputedSingleMasks", "precompute_single_masks",
+    "AttentionPairBias", "PairformerLayerV1", "PairformerLayerV2", "PairformerModule", "PrecomputedSingleMasks", "precompute_single_masks",
     "register_precompute_single_masks",
 ]

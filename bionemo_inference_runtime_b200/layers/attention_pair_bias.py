@@ -93,11 +93,25 @@ class AttentionPairBias(nn.Module):
         self.proj_o = Linear(c_s, c_s, bias=out_bias, dtype=dtype, skip_create_weights=skip_create_weights)
         self._folded = None
         self._folded_state = None
+        self._input_norm: list[nn.LayerNorm] = []  # a caller's LayerNorm of s folded into in_proj (not a submodule)
         self.register_load_state_dict_post_hook(_refold_after_load_state_dict)
 
     # ---- weights -----------------------------------------------------------------------------
+    def set_input_norm(self, norm: nn.LayerNorm | None) -> None:
+        """Fold a LayerNorm that the caller applies to ``s`` before this layer (the v2 pairformer layer's
+        ``pre_norm_s``) into the in-projection: ``forward`` then takes the un-normalised ``s``.  Only for layers
+        built without ``initial_norm``; the norm stays the caller's module (its parameters are read at fold time)."""
+        if norm is not None and self.norm_s is not None:
+            raise ValueError("a layer with initial_norm cannot fold a second LayerNorm")
+        self._input_norm = [] if norm is None else [norm]
+        self._folded = self._folded_state = None
+
+    def _norm_of_s(self) -> nn.LayerNorm | None:
+        return self.norm_s if self.norm_s is not None else (self._input_norm[0] if self._input_norm else None)
+
     def _params(self):
-        norm_s = (self.norm_s.weight, self.norm_s.bias) if self.norm_s is not None else (None, None)
+        norm = self._norm_of_s()
+        norm_s = (norm.weight, norm.bias) if norm is not None else (None, None)
         norm_z = (self.proj_z[0].weight, self.proj_z[0].bias) if len(self.proj_z) > 1 else (None, None)
         return (*norm_s, self.in_proj.weight, self.in_proj.bias, *norm_z, self.proj_z[-1].weight, self.proj_o.weight,
                 self.proj_o.bias)
@@ -191,7 +205,8 @@ class AttentionPairBias(nn.Module):
         w = self._weights(s.device)
         lengths = self._lengths(mask, mask_bias, B, N, s.device)
 
-        stats = ops.row_stats(s16, self.eps) if self.norm_s is not None else None
+        norm = self._norm_of_s()
+        stats = ops.row_stats(s16, norm.eps) if norm is not None else None
         planes = ensure_buffer(buffers, "pw_qkvg", (4, B, _HEADS, N, _PAD), torch.bfloat16, s.device)
         planes = ops.linear(s16, w["w_in"], w["sc_in"], ops.LINEAR_PLANES, B=B, rows=N, stats=stats, out=planes)
         bias = ensure_buffer(buffers, "pw_pair_bias", (B, _HEADS, N, ops.pad8(N)), torch.bfloat16, s.device)

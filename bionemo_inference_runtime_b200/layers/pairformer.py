@@ -1,7 +1,7 @@
 """Pairformer blocks on the sm_100a kernels.
 
-Counterparts of ``PairformerLayerV1``, ``PairformerNoSeqLayer``, ``PairformerNoSeqModule`` and ``PairformerModule``
-(``bionemo_ir/_torch/layers/transformers/pairformer.py:44-363`` and ``418-510``).  Per block the pair track runs
+Counterparts of ``PairformerLayerV1``, ``PairformerLayerV2``, ``PairformerNoSeqLayer``, ``PairformerNoSeqModule`` and
+``PairformerModule`` (``bionemo_ir/_torch/layers/transformers/pairformer.py:44-510``).  Per block the pair track runs
 triangle multiplication outgoing and incoming, triangle attention starting and ending node and the pair
 transition, every update added to ``z`` (``_transform_z``, lines 174-216 of the same file); the single track
 (``PairformerLayerV1.forward``, lines 218-252) then adds the attention with pair bias and the single transition to
@@ -116,6 +116,40 @@ class PairformerLayerV1(nn.Module):
         return s, z
 
 
+class PairformerLayerV2(PairformerLayerV1):
+    def __init__(self, post_layer_norm: bool = False, **kwargs):
+        """The v2 layer (pairformer.py:356-416): ``s + attention(pre_norm_s(s), z)``, the single transition and an
+        optional ``post_norm_s``.  ``pre_norm_s`` is folded into the attention's in-projection when the attention
+        has no initial norm of its own, so the single track stays the same five launches."""
+        super().__init__(**kwargs)
+        if self.no_update_s:
+            raise ValueError("the v2 layer updates the single representation; use PairformerNoSeqLayer otherwise")
+        self.post_layer_norm = post_layer_norm
+        self.pre_norm_s = nn.LayerNorm(self.token_s, dtype=torch.bfloat16)
+        self.post_norm_s = nn.LayerNorm(self.token_s, dtype=torch.bfloat16) if post_layer_norm else None
+        self._pre_norm_folded = self.attention.norm_s is None
+        if self._pre_norm_folded:
+            self.attention.set_input_norm(self.pre_norm_s)
+
+    def forward(self, s: torch.Tensor, z: torch.Tensor, mask: torch.Tensor, pair_mask: torch.Tensor,
+                trimul_metadata: TriangleMultiplicationMetadata,
+                attn_metadatas: dict[str, AttentionMetadata] | None = None,
+                precomputed_masks: PrecomputedPairMasks | None = None, precomputed_single_masks=None,
+                buffers: PreallocatedBuffers | None = None, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
+        z = self._transform_z(z, pair_mask, trimul_metadata, attn_metadatas, precomputed_masks=precomputed_masks,
+                              buffers=buffers, inplace_safe=bool(kwargs.get("inplace_safe", False)))
+        s_dtype = s.dtype
+        s16 = s.to(torch.bfloat16)
+        s_in = s16 if self._pre_norm_folded else self.pre_norm_s(s16)
+        s16 = self.attention(s_in, z, mask, attn_metadata=(attn_metadatas or {}).get("pairwise_attn"),
+                             mask_bias=getattr(precomputed_single_masks, "mask_bias", None), buffers=buffers,
+                             residual=s16)
+        s16 = self.transition_s(s16, residual=True, inplace=True)
+        if self.post_norm_s is not None:
+            s16 = self.post_norm_s(s16)
+        return s16.to(s_dtype), z
+
+
 class PairformerNoSeqLayer(PairformerLayerV1):
     def __init__(self, *, layer_idx: int, **kwargs):
         """The layer without the single track (pairformer.py:255-306); arguments as :class:`PairformerLayerV1`."""
@@ -144,9 +178,9 @@ class PairformerModule(nn.Module):
                       "attention_initial_norm": "attention_initial_norm",
                       "trimul_high_precision": "trimul_high_precision",
                       "trimul_mean_normalization": "trimul_mean_normalization", "s_path_dtype": "s_path_dtype",
-                      "tri_attn_transposed_bias": "tri_attn_transposed_bias"}
+                      "tri_attn_transposed_bias": "tri_attn_transposed_bias", "post_layer_norm": "post_layer_norm"}
 
-    def __init__(self, config=None, use_cuda_graph: bool = False, **kwargs):
+    def __init__(self, config=None, use_cuda_graph: bool = False, version: str = "v1", **kwargs):
         """``use_cuda_graph`` (not in the reference, whose graph capture lives in its runtime) records one forward
         of the whole stack per input shape and replays it; inputs are copied into the graph's buffers."""
         super().__init__()
@@ -155,14 +189,18 @@ class PairformerModule(nn.Module):
         self._graph_key = None
         self._graph_io = None
         if config is not None:
-            if getattr(config, "version", "v1") != "v1":
-                raise ValueError("only the v1 pairformer layer is built on the sm_100a kernels")
+            version = getattr(config, "version", version)
             for field, name in self._CONFIG_FIELDS.items():
                 if hasattr(config, field):
                     kwargs.setdefault(name, getattr(config, field))
         num_blocks = kwargs.pop("num_blocks", 8)
+        if version not in ("v1", "v2"):
+            raise ValueError(f"unknown pairformer layer version {version!r}")
+        if version == "v1":
+            kwargs.pop("post_layer_norm", None)  # the reference passes it to both; only v2 reads it
+        layer_cls = PairformerLayerV1 if version == "v1" else PairformerLayerV2
         self.config = config
-        self.layers = nn.ModuleList([PairformerLayerV1(layer_idx=i, **kwargs) for i in range(num_blocks)])
+        self.layers = nn.ModuleList([layer_cls(layer_idx=i, **kwargs) for i in range(num_blocks)])
         self.pair_mask_left_aligned = self.layers[0].pair_mask_left_aligned if self.layers else False
 
     def forward(self, s: torch.Tensor, z: torch.Tensor, mask: torch.Tensor, pair_mask: torch.Tensor,

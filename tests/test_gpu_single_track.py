@@ -232,3 +232,36 @@ def test_pairformer_module_graph_replay_matches_eager():
         assert torch.equal(got_s, want_s) and torch.equal(got_z, want_z)
         outs.append(got_s)
     assert not torch.equal(outs[0], outs[1])
+
+
+def test_v2_layer_equals_v1_with_the_pre_norm_as_initial_norm_and_applies_the_post_norm():
+    torch.manual_seed(8)
+    N = 48
+    kw = dict(num_blocks=1, dtype=torch.bfloat16, trimul_high_precision=False)
+    v1 = b200.PairformerModule(attention_initial_norm=True, **kw).to(DEV)
+    gen = torch.Generator(device=DEV).manual_seed(12)
+    for name, prm in v1.named_parameters():
+        if prm.dim() == 2:
+            prm.data.copy_(torch.randn(prm.shape, generator=gen, device=DEV) * 0.03)
+        else:
+            prm.data.copy_((0.0 if name.endswith("bias") else 1.0) + 0.1 * torch.randn(prm.shape, generator=gen, device=DEV))
+    sd = {k.replace("attention.norm_s", "pre_norm_s"): v for k, v in v1.state_dict().items()}
+    v2 = b200.PairformerModule(version="v2", **kw).to(DEV)
+    v2.load_state_dict(sd, strict=True)
+    m = (torch.arange(N, device=DEV) < 41).float()[None]
+    pair_mask = m[:, :, None] * m[:, None, :]
+    s = torch.randn(1, N, 384, device=DEV).bfloat16()
+    z = torch.randn(1, N, N, 128, device=DEV).bfloat16()
+    s1, z1 = v1(s.clone(), z.clone(), m, pair_mask)
+    s2, z2 = v2(s.clone(), z.clone(), m, pair_mask)
+    _ok()
+    assert torch.equal(z1, z2) and torch.equal(s1, s2)
+    # an attention with its own initial norm keeps the pre-norm as a separate step; with unit pre-norm weights the
+    # result is attention(LN(LN(s))) and stays finite; the post norm normalises the rows of the result
+    post = b200.PairformerModule(version="v2", post_layer_norm=True, **kw).to(DEV)
+    sd_post = dict(sd)
+    sd_post.update({"layers.0.post_norm_s.weight": torch.ones(384), "layers.0.post_norm_s.bias": torch.zeros(384)})
+    post.load_state_dict(sd_post, strict=True)
+    s3, _ = post(s.clone(), z.clone(), m, pair_mask)
+    _ok()
+    torch.testing.assert_close(s3.float(), F.layer_norm(s2.float(), (384,)), rtol=2e-2, atol=2e-2)

@@ -314,3 +314,22 @@ def test_single_mask_precompute_registry_and_key_counts():
                  dict(mask=None, mask_bias=cnt.mask_bias)):
         assert layer._lengths(form["mask"], form["mask_bias"], 2, 5, dev).tolist() == [3, 5]
     assert layer._lengths(None, None, 2, 5, dev).tolist() == [5, 5]
+
+
+def test_v2_pairformer_layer_names_and_pre_norm_fold():
+    """PairformerLayerV2 (bionemo_ir/_torch/layers/transformers/pairformer.py:356-416): pre_norm_s / post_norm_s."""
+    stack = b200.PairformerModule(num_blocks=1, version="v2", dtype=torch.bfloat16, post_layer_norm=True)
+    keys = set(stack.state_dict())
+    assert {"layers.0.pre_norm_s.weight", "layers.0.pre_norm_s.bias", "layers.0.post_norm_s.weight",
+            "layers.0.post_norm_s.bias"} <= keys
+    layer = stack.layers[0]
+    assert isinstance(layer, b200.PairformerLayerV2) and layer.attention.norm_s is None
+    assert layer.attention._norm_of_s() is layer.pre_norm_s          # folded into the in-projection
+    assert not any("_input_norm" in k for k in keys)                 # and not registered twice
+    own_norm = b200.PairformerModule(num_blocks=1, version="v2", attention_initial_norm=True).layers[0]
+    assert own_norm.attention._norm_of_s() is own_norm.attention.norm_s and not own_norm._pre_norm_folded
+    assert isinstance(b200.PairformerModule(num_blocks=1, post_layer_norm=True).layers[0], b200.PairformerLayerV1)
+    with pytest.raises(ValueError):
+        b200.PairformerModule(num_blocks=1, version="v3")
+    with pytest.raises(ValueError):
+        b200.PairformerLayerV2(no_update_s=True)
