@@ -166,11 +166,13 @@ class ShardedPairBlock:
         self.fused_transpose = fused_transpose
         self._cols: _PeerShard | None = None
         self._rows: _PeerShard | None = None
+        self._flag: torch.Tensor | None = None
 
     def _barrier(self, device) -> None:
         """Orders the peer stores against the other ranks' reads: a one-element all-reduce on the current stream."""
-        flag = torch.zeros(1, dtype=torch.int32, device=device)
-        dist.all_reduce(flag, group=self.group)
+        if self._flag is None or self._flag.device != torch.device(device):
+            self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        dist.all_reduce(self._flag, group=self.group)
 
     def _start_node_into_column_shards(self, z_rows: torch.Tensor, lengths_rows) -> torch.Tensor:
         """The starting node on the ROWS shard with its output written directly into every rank's COLS shard."""
