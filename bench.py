@@ -26,6 +26,7 @@ import subprocess
 import sys
 import threading
 import time
+import types
 from pathlib import Path
 
 import torch
@@ -169,9 +170,30 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
-def make_inputs(cfg: dict, seed: int, device):
-    from oracle import triangle_oracle as orc  # weight recipe only (seeded generators); nothing is computed with it
+# Seeded random weights of the benchmark's modules (matrices ~N(0, 0.02²), LayerNorm at identity, as BASELINE's
+# configs describe them), under the attribute names the module builders below read.
+def node_weights(seed: int) -> types.SimpleNamespace:
+    g = torch.Generator().manual_seed(seed)
+    return types.SimpleNamespace(w_bias=torch.randn(4, 128, generator=g) * 0.02, w_in=torch.randn(512, 128, generator=g) * 0.02,
+                                 w_out=torch.randn(128, 128, generator=g) * 0.02, ln_w=torch.ones(128),
+                                 ln_b=torch.zeros(128), b_in=None, b_out=None)
 
+
+def transition_weights(seed: int) -> types.SimpleNamespace:
+    g = torch.Generator().manual_seed(seed)
+    return types.SimpleNamespace(w1=torch.randn(1024, 128, generator=g) * 0.02, w2=torch.randn(128, 512, generator=g) * 0.02,
+                                 ln_w=torch.ones(128), ln_b=torch.zeros(128))
+
+
+def trimul_weights(seed: int) -> types.SimpleNamespace:
+    g = torch.Generator().manual_seed(seed)
+    return types.SimpleNamespace(w_p_in=torch.randn(256, 128, generator=g) * 0.02, w_g_in=torch.randn(256, 128, generator=g) * 0.02,
+                                 w_p_out=torch.randn(128, 128, generator=g) * 0.02, w_g_out=torch.randn(128, 128, generator=g) * 0.02,
+                                 ln_in_w=torch.ones(128), ln_in_b=torch.zeros(128), ln_out_w=torch.ones(128),
+                                 ln_out_b=torch.zeros(128))
+
+
+def make_inputs(cfg: dict, seed: int, device):
     gen = torch.Generator().manual_seed(seed)
     B, N = cfg["B"], cfg["N"]
     z = torch.randn(B, N, N, 128, generator=gen).to(torch.bfloat16)
@@ -180,10 +202,7 @@ def make_inputs(cfg: dict, seed: int, device):
     for b, L in enumerate(lens):
         m[b, :L] = 1
     mask = m[:, :, None] * m[:, None, :]
-    w_start = orc.make_node_weights(seed + 1)
-    w_end = orc.make_node_weights(seed + 2)
-    w_tr = orc.make_transition_weights(seed + 3)
-    return z, mask, lens, w_start, w_end, w_tr
+    return z, mask, lens, node_weights(seed + 1), node_weights(seed + 2), transition_weights(seed + 3)
 
 
 def build_modules(w_start, w_end, w_tr, device):
@@ -205,11 +224,10 @@ def build_modules(w_start, w_end, w_tr, device):
 
 def build_trimul(seed: int, device):
     import bionemo_inference_runtime_b200 as b200
-    from oracle import triangle_oracle as orc  # weight recipe only
 
     nodes = []
     for k, kind in enumerate((b200.TriangleMultiplicationNodeType.OUTGOING, b200.TriangleMultiplicationNodeType.INCOMING)):
-        w = orc.make_trimul_weights(seed + 10 + k)
+        w = trimul_weights(seed + 10 + k)
         n = b200.TriangleMultiplicationNode(multiplication_type=kind, dtype=torch.bfloat16, high_precision=False)
         n.load_state_dict({"norm_in.weight": w.ln_in_w, "norm_in.bias": w.ln_in_b, "p_in.weight": w.w_p_in,
                            "g_in.weight": w.w_g_in, "norm_out.weight": w.ln_out_w, "norm_out.bias": w.ln_out_b,
@@ -478,8 +496,6 @@ def run_sharded(args) -> dict:
 
     import bionemo_inference_runtime_b200 as b200
     from bionemo_inference_runtime_b200 import _lib, ops, sharded
-    from oracle import triangle_oracle as orc  # seeded weight recipe only
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -499,8 +515,8 @@ def run_sharded(args) -> dict:
 
     blocks = []
     for k in range(nblocks):
-        start, end, trans = build_modules(orc.make_node_weights(3000 + 3 * k), orc.make_node_weights(3001 + 3 * k),
-                                          orc.make_transition_weights(3002 + 3 * k), device)
+        start, end, trans = build_modules(node_weights(3000 + 3 * k), node_weights(3001 + 3 * k),
+                                          transition_weights(3002 + 3 * k), device)
         blocks.append((start, end, trans))
     if world > 1:
         fused = args.exchange == "peer_stores"
@@ -627,6 +643,8 @@ def cpu_sample(cfg: dict, rows: int, threads: int):
 
     torch.set_num_threads(threads)
     z, mask, lens, w_start, w_end, w_tr = make_inputs(cfg, 1000, "cpu")
+    w_start, w_end = (orc.NodeWeights(w.ln_w, w.ln_b, w.w_bias, w.w_in, w.b_in, w.w_out, w.b_out) for w in (w_start, w_end))
+    w_tr = orc.TransitionWeights(w_tr.ln_w, w_tr.ln_b, w_tr.w1, w_tr.w2)
     B, N = cfg["B"], cfg["N"]
     items = min(B, 2)
     z, mask = z[:items].float(), mask[:items]
