@@ -265,3 +265,33 @@ def test_v2_layer_equals_v1_with_the_pre_norm_as_initial_norm_and_applies_the_po
     s3, _ = post(s.clone(), z.clone(), m, pair_mask)
     _ok()
     torch.testing.assert_close(s3.float(), F.layer_norm(s2.float(), (384,)), rtol=2e-2, atol=2e-2)
+
+
+def test_single_track_entry_points_refuse_bad_arguments():
+    x = torch.zeros(1, 8, 384, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(384, 384, dtype=torch.bfloat16, device=DEV)
+    sc = torch.zeros(384, 2, device=DEV)
+    with pytest.raises(ValueError):  # K must be a multiple of 128
+        ops.linear(torch.zeros(1, 8, 200, dtype=torch.bfloat16, device=DEV), torch.zeros(384, 200, dtype=torch.bfloat16, device=DEV),
+                   sc, ops.LINEAR_ROWS, B=1, rows=8)
+    with pytest.raises(ValueError):  # the head-major form needs the 2048 columns of 4 planes x 16 heads x 32
+        ops.linear(x, w, sc, ops.LINEAR_PLANES, B=1, rows=8)
+    with pytest.raises(ValueError):  # a residual only with the row form
+        _lib.call("b200ta_linear", x.data_ptr(), 8 * 384, 384, 128, w.data_ptr(), sc.data_ptr(), None, x.data_ptr(), 384,
+                  x.data_ptr(), 192, 0, ops.LINEAR_SWIGLU, 1, 8, 384, 384, torch.cuda.current_stream().cuda_stream)
+    with pytest.raises(ValueError):
+        ops.linear(x, w, sc, 7, B=1, rows=8)
+    with pytest.raises(ValueError):  # row statistics hold a row in registers: K <= 2048
+        ops.row_stats(torch.zeros(4, 4096, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(ValueError):  # an odd head count
+        ops.pack_pair_bias_weights(None, None, torch.zeros(3, 128, device=DEV), 1.0)
+    z = torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16, device=DEV)
+    packed = ops.pack_pair_bias_weights(None, None, torch.zeros(16, 128, device=DEV), 1.0)
+    with pytest.raises(ValueError):  # the bias buffer must carry the padded key axis
+        ops.pair_bias(z, packed, 16, bias=torch.zeros(1, 16, 8, 9, dtype=torch.bfloat16, device=DEV))
+    # without a LayerNorm in the pack the projection runs on z as it is
+    w_z = torch.randn(16, 128, device=DEV) * 0.05
+    zr = torch.randn(1, 8, 8, 128, device=DEV).bfloat16()
+    got = ops.pair_bias(zr, ops.pack_pair_bias_weights(None, None, w_z, 2.0), 16)
+    _ok()
+    torch.testing.assert_close(got.float(), 2.0 * F.linear(zr.float(), w_z).movedim(-1, 1), **TOL)
