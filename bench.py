@@ -1,6 +1,7 @@
 """Benchmark of the triangle-attention hot path (starting node, then ending node) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2|cfg3|n768]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg2|cfg3|n768|block768|cfg4pair|cfg4|cfg5] [--blocks M] [--exchange all_to_all|peer_stores]
 
 One "step" is one pass of the hot path over one batch of synthetic pair tensors: the starting-node and the
 ending-node TriangleAttention (LayerNorm, q/k/v/gate + triangle-bias projections, masked biased attention, sigmoid
@@ -11,6 +12,11 @@ Metric: tri-attn TFLOP/s = algorithmic flops of the step (valid positions only) 
 line.  `value` is timed with CUDA events with inputs resident in HBM and L2 flushed between steps; `e2e` runs the
 same step through the module API from pinned host memory and back.  With N > 1 every rank processes its own batch
 (independent pair tensors, no data-path collective): weak scaling.
+
+Other workloads: "block768" adds the two triangle multiplications (the pair track of one Pairformer block),
+"cfg4pair" / "cfg4" replay a 48-block trunk without / with the single track from one CUDA graph (`--blocks`
+overrides the depth), and "cfg5" runs 4 attention blocks on one z[1, 4096, 4096, 128] row-sharded over the ranks
+(strong scaling; `--exchange` selects how the two transposes per block cross the links).
 
 --impl reference times the CPU restatement of the reference's eager path (oracle/) on the host cores, on a
 bounded row sample of the same workload.
