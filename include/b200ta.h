@@ -123,7 +123,7 @@ int b200ta_prologue(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s, con
 /*
  * Pair bias of the single-track attention: bias[b,h,q,k] = bias_scale * ( LayerNorm(z[b,q,k,:]) · W_z[h,:] ) for up
  * to 16 heads, written head-major with the key axis padded: the projection, the moveaxis and the padding in one pass
- * over z (the prologue kernel in its bias-only form, one N=16 tcgen05 GEMM per 128-position tile).
+ * over z (a streaming kernel of its own: six-stage TMA ring, one N=16 tcgen05 GEMM per 128-position tile).
  *
  *   b200ta_pack_pair_bias_weights: ln_w, ln_b [128] (both NULL: z is used as it is), w_z [num_heads,128] in
  *       weight_dtype; bias_scale multiplies the result (pass 1/softmax_scale for b200ta_attention);
