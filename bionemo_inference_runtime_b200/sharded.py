@@ -176,7 +176,7 @@ class ShardedPairBlock:
 
     def _start_node_into_column_shards(self, z_rows: torch.Tensor, lengths_rows) -> torch.Tensor:
         """The starting node on the ROWS shard with its output written directly into every rank's COLS shard."""
-        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        rank = dist.get_rank(self.group)
         B, n, N, c = z_rows.shape
         if self._cols is None or self._cols.shape != (B, N, n, c):
             self._cols = self.stages.peer_shard((B, N, n, c), z_rows.device, self.group)
@@ -184,8 +184,8 @@ class ShardedPairBlock:
         qkvg, bias_local = self.stages.prologue(node, z_rows)
         bias_full = gather_bias(bias_local, self.group)
         og = self.stages.attention(node, qkvg, bias_full, lengths_rows, B, n, N)
-        # The bias all-gather above already orders this call after every rank's last read of its column shard (the
-        # exchange back to rows, or the caller's use of a ``keep_layout`` result, precedes its next call).
+        # Every rank's last read of its column shard lies before a collective this rank has already completed: the
+        # barrier after the previous call's transition, or its exchange back to rows, and the bias all-gather above.
         self.stages.epilogue_scatter(node, og, z_rows, self._cols, rank)
         self._barrier(z_rows.device)  # every rank's stores into this rank's column shard have landed
         return self._cols.tensor
