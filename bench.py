@@ -640,7 +640,7 @@ def run_sharded(args) -> dict:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per attention launch, from the committed ncu summaries (profiles/)
-TRAFFIC: dict[str, float | None] = {"cfg2": 331.3e6, "cfg3": None, "n768": None}
+TRAFFIC: dict[str, float | None] = {"cfg2": 341.5e6, "cfg3": None, "n768": None}
 
 
 def cpu_sample(cfg: dict, rows: int, threads: int):
