@@ -255,6 +255,7 @@ def run_ours(args) -> dict:
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+    numa_cores = b200.bind_to_gpu_numa_node(device) if world > 1 else None  # pinned buffers next to this rank's GPU
     cfg = dict(WORKLOADS[args.workload])
     if args.blocks is not None and cfg.get("blocks") and not cfg.get("sharded"):
         cfg["blocks"] = args.blocks
@@ -477,7 +478,8 @@ def run_ours(args) -> dict:
         "e2e": {"value": flops_all / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": bytes_io, "d2h_bytes_per_step": bytes_io,
                 "mode": "HostPipeline depth 2: copies of neighbouring steps overlap the compute",
-                "single_step_latency_ms": e2e_serial_ms},
+                "single_step_latency_ms": e2e_serial_ms,
+                "host_cores_per_rank": None if numa_cores is None else len(numa_cores)},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"kernel": "attention_kernel", "bound": "tensor", "achieved": attn_flops / attn_ms / 1e9,
                      "peak": peak_tf, "unit": "TFLOP/s", "frac": attn_flops / attn_ms / 1e9 / peak_tf,

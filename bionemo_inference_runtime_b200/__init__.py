@@ -13,6 +13,6 @@ _lib.load()  # fail loudly at import when the extension has not been built
 from . import ops  # noqa: E402
 from .layers import *  # noqa: E402,F401,F403
 from .layers import __all__ as _layers_all  # noqa: E402
-from .host_pipeline import HostPipeline  # noqa: E402
+from .host_pipeline import HostPipeline, bind_to_gpu_numa_node  # noqa: E402
 
-__all__ = ["ops", "HostPipeline", *_layers_all]
+__all__ = ["ops", "HostPipeline", "bind_to_gpu_numa_node", *_layers_all]

@@ -8,9 +8,38 @@ The copies are plain ``cudaMemcpyAsync`` calls (one per batch) from and to pinne
 
 from __future__ import annotations
 
+import os
 from typing import Callable, Sequence
 
 import torch
+
+
+def bind_to_gpu_numa_node(device: torch.device | str | int) -> list[int] | None:
+    """Restrict this process to the CPU cores of the NUMA node the GPU hangs off, so that pinned buffers allocated
+    afterwards are local to the GPU's PCIe root and the copy threads run next to them.  With one process per GPU on
+    a two-socket host this keeps host-to-device copies off the socket interconnect.  Returns the core list, or
+    ``None`` when the topology cannot be read (nothing is changed then).  Host-side only: no GPU setting is touched.
+    """
+    try:
+        props = torch.cuda.get_device_properties(torch.device(device) if not isinstance(device, int) else device)
+        address = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{address}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            spec = f.read().strip()
+        cores: list[int] = []
+        for part in spec.split(","):
+            lo, _, hi = part.partition("-")
+            cores.extend(range(int(lo), int(hi or lo) + 1))
+        allowed = sorted(set(cores) & os.sched_getaffinity(0))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return allowed
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return None
 
 
 class HostPipeline:
