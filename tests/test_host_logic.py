@@ -333,3 +333,13 @@ def test_v2_pairformer_layer_names_and_pre_norm_fold():
         b200.PairformerModule(num_blocks=1, version="v3")
     with pytest.raises(ValueError):
         b200.PairformerLayerV2(no_update_s=True)
+
+
+def test_numa_binding_is_a_no_op_without_a_readable_topology():
+    before = sorted(__import__("os").sched_getaffinity(0))
+    cores = b200.bind_to_gpu_numa_node(0)  # no GPU here, or a container without NUMA nodes: nothing may change
+    if cores is None:
+        assert sorted(__import__("os").sched_getaffinity(0)) == before
+    else:
+        assert set(cores) <= set(before) and sorted(__import__("os").sched_getaffinity(0)) == cores
+        __import__("os").sched_setaffinity(0, before)
