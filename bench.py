@@ -1,25 +1,33 @@
-"""Benchmark of the triangle-attention hot path (starting node, then ending node) on B200.
+"""Benchmark of the triangle-attention hot path (starting node, ending node, pair transition) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload cfg2|cfg3|n768|block768|cfg4pair|cfg4|cfg5] [--blocks M] [--exchange all_to_all|peer_stores]
+                    [--workload cfg5|cfg2|cfg3|n768|block768|cfg4pair|cfg4] [--blocks M]
+                    [--exchange all_to_all|peer_stores] [--no-also] [--no-cpu-baseline]
 
 One "step" is one pass of the hot path over one batch of synthetic pair tensors: the starting-node and the
 ending-node TriangleAttention (LayerNorm, q/k/v/gate + triangle-bias projections, masked biased attention, sigmoid
 gate, output projection, residual) applied in sequence; workloads with a transition also run the fused pair
-transition.  Default workload ("cfg2"): z[1, 512, 512, 128] bf16, 475 valid tokens, weights ~N(0, 0.02²).
+transition.
+
+Default workload ("cfg5", the same at every N): 4 pair-track blocks (start node, transpose, end node, transition) on
+ONE pair tensor z[1, 4096, 4096, 128] bf16 with 3900 valid tokens, its pair rows sharded over the N ranks: strong
+scaling, `value` = total TFLOP/s of the job, so value_N / (N * value_1) is the parallel efficiency.  With N > 1 the
+run first checks the sharded block against the single-GPU modules on a small tensor (`sharded_check`) and exits
+non-zero when they disagree.  With N = 1 the same JSON line carries, under `also`, the single-GPU figures of
+"cfg2" (z[1, 512, 512, 128], 475 valid tokens, start + end node) and "n768" (z[1, 768, 768, 128], start + end node
++ transition), each with its own roofline.
 
 Metric: tri-attn TFLOP/s = algorithmic flops of the step (valid positions only) / time.  Rank 0 prints one JSON
-line.  `value` is timed with CUDA events with inputs resident in HBM and L2 flushed between steps; `e2e` runs the
-same step through the module API from pinned host memory and back.  With N > 1 every rank processes its own batch
-(independent pair tensors, no data-path collective): weak scaling.
+line.  `value` is timed with CUDA events with inputs resident in HBM (inputs far larger than L2, or L2 flushed
+between steps); `e2e` runs the same step through the module API from pinned host memory and back.
 
 Other workloads: "block768" adds the two triangle multiplications (the pair track of one Pairformer block),
 "cfg4pair" / "cfg4" replay a 48-block trunk without / with the single track from one CUDA graph (`--blocks`
-overrides the depth), and "cfg5" runs 4 attention blocks on one z[1, 4096, 4096, 128] row-sharded over the ranks
-(strong scaling; `--exchange` selects how the two transposes per block cross the links).
+overrides the depth); with N > 1 these non-sharded workloads run one independent batch per rank (weak scaling).
 
---impl reference times the CPU restatement of the reference's eager path (oracle/) on the host cores, on a
-bounded row sample of the same workload.
+--impl reference times the CPU implementation of the reference's eager path on the host cores, on a bounded row
+sample of the same workload: the reference's own modules when they have been staged next to the oracle, else the
+restatement in oracle/.
 """
 
 from __future__ import annotations
@@ -64,7 +72,8 @@ WORKLOADS = {
                  desc="4 x (start node, all-to-all, end node, transition), z[1,4096,4096,128] bf16 row-sharded over the "
                       "GPUs, 3900 valid tokens (BASELINE config 5)"),
 }
-DEFAULT_STEPS = {"cfg2": 100, "cfg3": 20, "n768": 50, "block768": 50, "cfg4pair": 5, "cfg4": 5, "cfg5": 3}
+DEFAULT_STEPS = {"cfg2": 100, "cfg3": 20, "n768": 50, "block768": 50, "cfg4pair": 5, "cfg4": 5, "cfg5": 5}
+ALSO_STEPS = 20  # timed steps of each extra single-GPU workload reported under "also"
 
 
 def valid_lengths(spec: str, B: int, N: int, gen: torch.Generator) -> list[int]:
@@ -242,7 +251,9 @@ def build_trimul(seed: int, device):
     return nodes
 
 
-def run_ours(args) -> dict:
+def run_ours(args, brief: bool = False) -> dict:
+    """Non-sharded workloads: one independent batch per rank.  ``brief`` (used for the extra workloads reported
+    beside the default one) skips the CPU baseline and the one-step-at-a-time latency loop."""
     import torch.distributed as dist
 
     from bionemo_inference_runtime_b200 import _lib, ops
@@ -383,7 +394,7 @@ def run_ours(args) -> dict:
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
     # the same path one step at a time (latency of a single pair tensor: copy in, compute, copy out)
     serial = []
-    for i in range(3 + min(args.steps, 20)):
+    for i in range(3 + (3 if brief else min(args.steps, 20))):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         pipe.run([z_pin], [outs_pin[0]])
@@ -488,17 +499,60 @@ def run_ours(args) -> dict:
     }
     if single_kernels is not None:
         result["single_track_kernels"] = single_kernels
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and not cfg.get("trimul"):  # the CPU sample covers rows of the attention nodes and the transition only
-        result["cpu_baseline"] = cpu_baseline(cfg, args.workload)
+    if rank == 0 and world == 1 and not brief and not args.no_cpu_baseline and not cfg.get("trimul"):
+        result["cpu_baseline"] = cpu_baseline(cfg, args.workload)  # rows of the attention nodes and the transition only
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return result if rank == 0 else {}
 
 
+NVLINK_GBS = 900.0  # per direction per GPU, the figure the config-5 roofline is defined on
+
+
+def sharded_check(args, world: int, rank: int, device) -> dict:
+    """The sharded block against the same modules on one GPU, on a tensor small enough to hold whole on rank 0:
+    z[1, 512, 512, 128], 475 valid tokens, one block, the exchange form the benchmark uses.  Every rank takes part;
+    rank 0 compares.  The block runs twice when the transposes are fused (the second call reuses the
+    symmetric-memory shards, as consecutive blocks of the benchmark do)."""
+    import torch.distributed as dist
+
+    from bionemo_inference_runtime_b200 import sharded
+
+    N, valid = 512, 475
+    n = N // world
+    z = torch.randn(1, N, N, 128, generator=torch.Generator().manual_seed(77)).bfloat16().to(device)
+    start, end, trans = build_modules(node_weights(7001), node_weights(7002), transition_weights(7003), device)
+    idx = torch.arange(rank * n, (rank + 1) * n, device=device)
+    lengths = torch.where(idx < valid, valid, 0).to(torch.int32).reshape(1, n)
+    fused = args.exchange == "peer_stores"
+    block = sharded.ShardedPairBlock(start, end, trans, fused_transpose=fused)
+    out_rows = block(sharded.shard(z, rank, world), lengths, lengths)
+    if fused:
+        out_rows = block(sharded.shard(z, rank, world), lengths, lengths)
+    gathered = [torch.empty_like(out_rows) for _ in range(world)]
+    dist.all_gather(gathered, out_rows)
+    verdict = torch.zeros(3, dtype=torch.float64, device=device)
+    if rank == 0:
+        full = torch.where(torch.arange(N, device=device) < valid, valid, 0).to(torch.int32).reshape(1, N)
+        want = start(z, mask_bias=full, residual=True)
+        want = end(want, mask_bias=full, residual=True)
+        want = trans(want, residual=True)
+        got = torch.cat(gathered, dim=1)
+        diff = (got.float() - want.float()).abs()
+        within = bool((diff <= 2e-2 + 2e-2 * want.float().abs()).all())
+        verdict[0], verdict[1], verdict[2] = float(torch.equal(got, want)), float(diff.max()), float(within)
+    dist.broadcast(verdict, src=0)
+    torch.cuda.synchronize()
+    del block
+    return {"equal": bool(verdict[0].item()), "max_abs_diff": verdict[1].item(), "within_bf16_tolerance": bool(verdict[2].item()),
+            "tolerance": "rtol = atol = 2e-2", "exchange": args.exchange, "tokens": N, "valid": valid, "blocks": 1,
+            "against": "the same modules on rank 0 alone"}
+
+
 def run_sharded(args) -> dict:
     """Benchmark config 5: one pair tensor z[1, 4096, 4096, 128] (3900 valid tokens) row-sharded over the ranks,
-    4 pair-track blocks of start node -> all-to-all -> end node -> transition (-> all-to-all back).  The total work
+    4 pair-track blocks of start node -> transpose -> end node -> transition (-> transpose back).  The total work
     is fixed (strong scaling); with one rank the same blocks run on the whole tensor without any exchange."""
     import torch.distributed as dist
 
@@ -513,6 +567,18 @@ def run_sharded(args) -> dict:
         dist.init_process_group("nccl", device_id=device)
     cfg = WORKLOADS[args.workload]
     N, valid, nblocks = cfg["N"], int(cfg["valid"]), cfg["blocks"]
+    if N % world:
+        raise SystemExit(f"{N} pair rows do not divide over {world} ranks")
+    check = None
+    if world > 1:
+        check = sharded_check(args, world, rank, device)
+        if not check["within_bf16_tolerance"]:
+            if rank == 0:
+                print(json.dumps({"sharded_check": check, "error": "sharded block differs from the single-GPU modules"}),
+                      flush=True)
+            dist.barrier()
+            dist.destroy_process_group()
+            raise SystemExit(3)
     n = N // world
     gen = torch.Generator(device=device).manual_seed(2000 + rank)
     z_rows = torch.empty(1, n, N, 128, dtype=torch.bfloat16, device=device)
@@ -544,7 +610,8 @@ def run_sharded(args) -> dict:
                 z = t(z, residual=True, inplace=True)
             return z
 
-    flops_total = nblocks * (2 * node_flops(valid) + transition_flops(valid))
+    flops_block = 2 * node_flops(valid) + transition_flops(valid)
+    flops_total = nblocks * flops_block
     launches = nblocks * 7
 
     def barrier():
@@ -587,6 +654,7 @@ def run_sharded(args) -> dict:
         if i >= 1:
             e2e_times.append((time.perf_counter() - t0) * 1e3)
     e2e_ms = sum(e2e_times) / len(e2e_times)
+    del zd
 
     # dominant kernel on this rank's shard of the first block's starting node
     start = blocks[0][0]
@@ -606,7 +674,8 @@ def run_sharded(args) -> dict:
             ktimes.append(e0.elapsed_time(e1))
     attn_ms = sum(ktimes) / len(ktimes)
     attn_flops = float((lengths_local > 0).sum().item()) * valid * 512.0 * valid
-    peak_tf, _, peak_kind = measured_peaks()
+    del qkvg, og, bias_full, bias_loc
+    peak_tf, peak_gbs, peak_kind = measured_peaks()
 
     stats = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
     if world > 1:
@@ -614,31 +683,66 @@ def run_sharded(args) -> dict:
     ms, e2e_ms = stats.tolist()
     shard_bytes = z_rows.numel() * 2
     a2a_bytes = 0 if world == 1 else int(shard_bytes * (world - 1) / world)
+    # roofline of one block as the configuration defines it: the slower of (flops at the bf16 peak, compulsory bytes
+    # at the copy bandwidth) per GPU, plus the bytes of the two transposes at the link bandwidth
+    block_ms = ms / nblocks
+    t_flops = flops_block / world / (peak_tf * 1e12) * 1e3
+    t_bytes = 3 * 512.0 * N * N / world / (peak_gbs * 1e9) * 1e3  # three modules, 512 B per position each
+    t_links = 2 * a2a_bytes / (NVLINK_GBS * 1e9) * 1e3
+    t_roof = max(t_flops, t_bytes) + t_links
+    if world > 1:
+        transposes = ("rows->columns by peer stores from the starting node's output kernel, columns->rows by peer TMA "
+                      "stores from the transition kernel" if args.exchange == "peer_stores" else "2 NCCL all-to-all")
+        collectives = (f"per block: 2 all-gathers of the triangle bias ({N * ops.pad8(N) * 4 * 2} B in total each)"
+                       + (" and 2 one-element all-reduces that order the peer stores" if args.exchange == "peer_stores"
+                          else " and 2 all-to-all of the shard"))
+        parallelism = f"pair rows sharded x{world}; {transposes}; {a2a_bytes} B per rank and transpose cross the links"
+    else:
+        collectives, parallelism = "none", "pair rows sharded x1 (single GPU, no exchange)"
     result = {
         "metric": "tri_attn_tflops", "value": flops_total / ms / 1e9, "unit": "TFLOP/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "ms_per_step_median": ms_median,
+        "ms_per_step_min": ms_min, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {cfg['desc']}", "tokens": N, "valid_lengths": cfg["valid"],
-                   "blocks": nblocks, "block_ms": ms / nblocks, "l2": "inputs far larger than L2 (4.3 GB pair tensor)",
-                   "empty_row_mode": "uniform",
-                   "parallelism": (f"pair rows sharded x{world}; per block "
-                                   + ("1 transpose by peer stores from the output kernel and 1 all-to-all"
-                                      if args.exchange == "peer_stores" else "2 all-to-all")
-                                   + f" of {a2a_bytes} B per rank and 2 all-gathers of the triangle bias")
-                   if world > 1 else "single GPU, no exchange"},
+                   "blocks": nblocks, "block_ms": block_ms, "l2": "inputs far larger than L2 (4.3 GB pair tensor)",
+                   "empty_row_mode": "uniform", "parallelism": parallelism, "collectives": collectives},
         "e2e": {"value": flops_total / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": shard_bytes, "d2h_bytes_per_step": shard_bytes},
+                "h2d_bytes_per_step": shard_bytes, "d2h_bytes_per_step": shard_bytes,
+                "mode": "each rank copies its row shard in from pinned host memory, runs the 4 blocks, copies it back"},
         "gpu_launches": launches * args.steps,
         "roofline": {"kernel": "attention_kernel", "bound": "tensor", "achieved": attn_flops / attn_ms / 1e9,
                      "peak": peak_tf, "unit": "TFLOP/s", "frac": attn_flops / attn_ms / 1e9 / peak_tf,
-                     "peak_source": f"{peak_kind} bf16 burst", "ms_per_launch": attn_ms, "traffic": None,
-                     "note": "rank 0's shard of one starting node"},
+                     "peak_source": f"{peak_kind} bf16 burst", "ms_per_launch": attn_ms,
+                     "traffic": TRAFFIC.get(args.workload),
+                     "note": "rank 0's shard of one starting node; algorithmic flops = 512 x valid keys per valid position"},
+        "roofline_block": {"definition": "max(flops / bf16 peak, 3 x 512 B per position / HBM) per GPU + bytes of the two "
+                                         "transposes / 900 GB/s", "flops_ms": t_flops, "hbm_ms": t_bytes,
+                           "links_ms": t_links, "roofline_ms": t_roof, "block_ms": block_ms, "frac": t_roof / block_ms,
+                           "peaks": f"{peak_kind}: {peak_tf} TFLOP/s bf16 burst, {peak_gbs} GB/s copy; NVLink nominal"},
         "clocks": clocks.summary(),
     }
+    if check is not None:
+        result["sharded_check"] = check
+    del work, z_rows, z_pin, out_pin, blocks
+    torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    return result if rank == 0 else {}
+    if rank != 0:
+        return {}
+    if world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline_rows_scaled(cfg, args.workload)
+    if world == 1 and not args.no_also:
+        result["also"] = {}
+        for name in ("cfg2", "n768"):
+            sub = argparse.Namespace(**{**vars(args), "workload": name, "steps": ALSO_STEPS, "blocks": None})
+            r = run_ours(sub, brief=True)
+            result["also"][name] = {k: r[k] for k in ("value", "unit", "steps", "ms_per_step", "ms_per_step_median",
+                                                      "ms_per_step_cuda_graph_warm_l2", "config", "e2e", "gpu_launches",
+                                                      "roofline", "clocks")}
+            torch.cuda.empty_cache()
+    return result
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per attention launch, from the committed ncu summaries (profiles/)
@@ -689,27 +793,105 @@ def cpu_baseline(cfg: dict, name: str, rows: int = 128, budget_s: float = 12.0) 
                       f"{' + transition' if cfg['transition'] else ''}, fp32 eager restatement (oracle/), torch CPU"}
 
 
+class CpuRowSampler:
+    """The CPU restatement on a row sample of a workload too large to run whole on the host (config 5: the eager
+    path's logits alone would need 1.1 TB).  The triangle bias of ALL pair rows is computed once per node (that is
+    whole-node work and is timed as such); a step then runs ``rows`` sampled pair rows of both nodes and of the
+    transition, in chunks of 16 rows, and the node time is extrapolated as bias + rows-time x N / rows (the eager
+    path computes every row, padded ones included; rows are independent given the bias)."""
+
+    def __init__(self, cfg: dict, threads: int):
+        from oracle import triangle_oracle as orc
+
+        self.orc, self.cfg = orc, cfg
+        torch.set_num_threads(threads)
+        N, valid = cfg["N"], int(cfg["valid"])
+        self.N, self.valid = N, valid
+        slab = torch.randn(1, 256, N, 128, generator=torch.Generator().manual_seed(1000)).bfloat16()
+        self.z = slab.repeat(1, N // 256, 1, 1)  # z ~ N(0,1), a seeded 256-row slab tiled to N rows (4.3 GB in bf16)
+        ws, we, wt = node_weights(3000), node_weights(3001), transition_weights(3002)
+        self.w = [orc.NodeWeights(w.ln_w, w.ln_b, w.w_bias, w.w_in, w.b_in, w.w_out, w.b_out) for w in (ws, we)]
+        self.wt = orc.TransitionWeights(wt.ln_w, wt.ln_b, wt.w1, wt.w2)
+        self.m = (torch.arange(N) < valid).float()
+        t0 = time.perf_counter()
+        self.tb = [orc.triangle_bias(self.z, self.w[k], k) for k in (orc.STARTING, orc.ENDING)]
+        self.bias_s = time.perf_counter() - t0  # both nodes, all rows
+        self.cursor = 0
+
+    def step(self, rows: int) -> float:
+        orc, N = self.orc, self.N
+        sel = (torch.arange(rows) * (N // rows) + self.cursor) % N  # spread over valid and padded rows alike
+        self.cursor += 1
+        t0 = time.perf_counter()
+        for c0 in range(0, rows, 16):
+            r = sel[c0:c0 + 16]
+            mk = (self.m[r, None] * self.m[None, :])[None]  # m (x) m restricted to the sampled rows
+            for k in (orc.STARTING, orc.ENDING):
+                orc.node_forward_rows(self.z, mk, self.w[k], k, r, residual=True, tri_bias=self.tb[k])
+            orc.transition_forward(self.z[:, r].float(), None, self.wt, residual=True)
+        return time.perf_counter() - t0
+
+    def flops_per_block(self) -> float:
+        return 2 * node_flops(self.valid) + transition_flops(self.valid)
+
+    def block_seconds(self, step_s: float, rows: int) -> float:
+        return self.bias_s + step_s * self.N / rows
+
+    def describe(self, rows: int, reps: int) -> str:
+        return (f"{reps} x ({rows} of {self.N} pair rows in chunks of 16, both nodes + transition) + the triangle bias "
+                f"of all rows once ({self.bias_s:.1f} s), extrapolated to one block as bias + rows-time x {self.N}/{rows}; "
+                "fp32 eager restatement (oracle/), torch CPU")
+
+
+def cpu_baseline_rows_scaled(cfg: dict, name: str, rows: int = 16, budget_s: float = 12.0) -> dict:
+    threads = os.cpu_count() or 1
+    sampler = CpuRowSampler(cfg, threads)
+    sampler.step(16)  # warm the thread pool and the allocator
+    dt, reps = 0.0, 0
+    while dt < budget_s and reps < 16:
+        dt += sampler.step(rows)
+        reps += 1
+    block_s = sampler.block_seconds(dt / reps, rows)
+    return {"value": sampler.flops_per_block() / block_s / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "seconds": dt + sampler.bias_s, "extrapolated_block_seconds": block_s,
+            "sample": f"{name}: " + sampler.describe(rows, reps)}
+
+
 def run_reference(args) -> dict:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return {}
     cfg = WORKLOADS[args.workload]
     threads = os.cpu_count() or 1
-    for _ in range(min(args.warmup, 1)):
-        cpu_sample(cfg, 32, threads)
-    fl = dt = 0.0
-    nrows = items = 0
-    for _ in range(args.steps):
-        f, d, nrows, items = cpu_sample(cfg, 48, threads)
-        fl += f
-        dt += d
-    value = fl / dt / 1e12
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    sample = (f"{args.workload}: {nrows} of {cfg['N']} pair rows of {items} item(s) per step, both nodes"
-              f"{' + transition' if cfg['transition'] else ''}, fp32 eager restatement (oracle/), torch CPU")
+    warmup = max(args.warmup, 0)
+    if cfg.get("sharded"):
+        rows = 8
+        sampler = CpuRowSampler(cfg, threads)
+        for _ in range(warmup):
+            sampler.step(rows)
+        dt = sum(sampler.step(rows) for _ in range(args.steps))
+        block_s = sampler.block_seconds(dt / args.steps, rows)
+        value = sampler.flops_per_block() / block_s / 1e12
+        sample = f"{args.workload}: " + sampler.describe(rows, args.steps)
+        ms_step = dt / args.steps * 1e3
+    else:
+        for _ in range(warmup):
+            cpu_sample(cfg, 48, threads)
+        fl = dt = 0.0
+        nrows = items = 0
+        for _ in range(args.steps):
+            f, d, nrows, items = cpu_sample(cfg, 48, threads)
+            fl += f
+            dt += d
+        value = fl / dt / 1e12
+        sample = (f"{args.workload}: {nrows} of {cfg['N']} pair rows of {items} item(s) per step, both nodes"
+                  f"{' + transition' if cfg['transition'] else ''}, fp32 eager restatement (oracle/), torch CPU")
+        ms_step = dt / args.steps * 1e3
     return {"impl": "reference", "metric": "tri_attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong" if cfg.get("sharded") else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {cfg['desc']}", "sampled": sample},
             "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -722,13 +904,15 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=None, help="timed steps (default depends on the workload)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg5")
     ap.add_argument("--blocks", type=int, default=None,
                     help="override the number of blocks of a stack workload (cfg4, cfg4pair), e.g. 1 for a profile")
     ap.add_argument("--exchange", choices=["all_to_all", "peer_stores"], default="peer_stores",
                     help="sharded workloads: how the rows->columns transpose crosses the links (NCCL all-to-all, or "
                          "stores from the starting node's output kernel into the peers' column shards)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-also", action="store_true",
+                    help="single-GPU run of the default workload: leave out the extra cfg2 / n768 figures")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = DEFAULT_STEPS[args.workload] if args.impl == "ours" else 5

@@ -48,7 +48,9 @@ class HostPipeline:
     ``fn`` is called on the compute stream with the device copy of one input and the index of the slot it
     occupies (``0 <= slot < depth``); whatever it returns must stay valid until the same slot is used again
     (e.g. a tensor from a per-slot buffer dict), because the copy-out of batch ``i`` runs while ``fn`` already
-    works on batch ``i+1``.  Inputs must all have the shape and dtype of ``example``.
+    works on batch ``i+1``.  ``fn`` may also work in place and return the slot tensor itself: the next copy into a
+    slot waits for the copy-out of the slot's previous result as well as for its compute.  Inputs must all have the
+    shape and dtype of ``example``.
     """
 
     def __init__(self, fn: Callable[[torch.Tensor, int], torch.Tensor], example: torch.Tensor,
@@ -83,6 +85,7 @@ class HostPipeline:
             with torch.cuda.stream(self.s_in):
                 if reused:
                     self.s_in.wait_event(self.cmp_done[k])  # the slot's previous batch has been consumed
+                    self.s_in.wait_event(self.out_done[k])  # ... and copied out, in case fn returned the slot itself
                 self.slots[k].copy_(src, non_blocking=True)
                 self.in_done[k].record(self.s_in)
             with torch.cuda.stream(self.s_cmp):

@@ -31,35 +31,30 @@ class WeightsLoadingConfig:
     segment_sizes: tuple[int, ...] = ()
 
 
-def _default_device() -> torch.device:
-    return torch.device("cuda") if torch.cuda.is_available() else torch.device("cpu")
-
-
 class Linear(nn.Module):
+    """``weight[out_features, in_features]`` and an optional ``bias[out_features]``, both frozen.  The tensors are
+    allocated (uninitialised, on the GPU when there is one) at construction unless ``skip_create_weights`` defers
+    that to a later ``create_weights()``."""
+
     def __init__(self, in_features: int, out_features: int, bias: bool = True, dtype: torch.dtype = None,
                  weights_loading_config: WeightsLoadingConfig | None = None, skip_create_weights: bool = False):
         super().__init__()
-        self.has_bias = bias
-        self.dtype = dtype
-        self.weights_loading_config = weights_loading_config or WeightsLoadingConfig()
-        self.in_features = in_features
-        self.out_features = out_features
+        self.in_features, self.out_features = in_features, out_features
+        self.has_bias, self.dtype = bias, dtype
+        self.weights_loading_config = WeightsLoadingConfig() if weights_loading_config is None else weights_loading_config
         self._weights_created = False
         if not skip_create_weights:
             self.create_weights()
 
+    def _frozen(self, *shape: int) -> Parameter:
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+        return Parameter(torch.empty(shape, dtype=self.dtype, device=device), requires_grad=False)
+
     def create_weights(self):
-        if self._weights_created:
-            return
-        device = _default_device()
-        self.weight = Parameter(torch.empty((self.out_features, self.in_features), dtype=self.dtype, device=device),
-                                requires_grad=False)
-        if self.has_bias:
-            self.bias = Parameter(torch.empty((self.out_features,), dtype=self.dtype, device=device),
-                                  requires_grad=False)
-        else:
-            self.register_parameter("bias", None)
-        self._weights_created = True
+        if not self._weights_created:
+            self.weight = self._frozen(self.out_features, self.in_features)
+            self.register_parameter("bias", self._frozen(self.out_features) if self.has_bias else None)
+            self._weights_created = True
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
         return F.linear(input, self.weight, self.bias)

@@ -32,6 +32,16 @@ def _row_mask(x: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
     return mask.expand(rows)
 
 
+def _storage_order(x: torch.Tensor) -> list[int] | None:
+    """The permutation of dimensions that makes ``x`` contiguous (channels stay last), or None when ``x`` is not a
+    permuted view of a dense tensor."""
+    if x.stride(-1) != 1:
+        return None
+    lead = sorted(range(x.dim() - 1), key=lambda d: (-x.stride(d), d))
+    order = lead + [x.dim() - 1]
+    return order if x.permute(order).is_contiguous() else None
+
+
 class Transition(nn.Module):
     def __init__(self, dim: int, hidden: int, out_dim: int | None = None, layer_idx: int = 0, eps: float = 1e-5,
                  dtype: torch.dtype = None, skip_create_weights: bool = False,
@@ -107,17 +117,25 @@ class Transition(nn.Module):
         if x.dtype != torch.bfloat16:
             x = x.to(torch.bfloat16)
             inplace = False
-        xc = x if x.is_contiguous() else x.contiguous()
+        if not x.is_contiguous():
+            # The transition is position-wise, so a permuted view (an ending node's transposed pair tensor, say) is
+            # processed in its storage order and the result handed back under the same permutation: no copy, and
+            # ``inplace`` still writes the caller's storage.
+            order = _storage_order(x)
+            if order is None:
+                raise ValueError("Transition takes a contiguous tensor or a permuted view of one (channels last, "
+                                 f"unit stride); got shape {tuple(x.shape)} with strides {x.stride()}")
+            inverse = [order.index(d) for d in range(x.dim())]
+            mask_p = None if mask is None else _row_mask(x, mask).permute(order[:-1])
+            y = self.forward(x.permute(order), mask_p, residual=residual, inplace=inplace)
+            return x if (residual and inplace) else y.permute(inverse)
+        xc = x
         if not self._fused:
             return self._forward_gemms(x, xc, mask, residual, inplace)
-        out = xc if (residual and inplace and xc is x) else None
+        out = xc if (residual and inplace) else None
         row_mask = None if mask is None else _row_mask(xc, mask)
-        y = ops.transition(xc, self._packed(x.device), row_mask, self.eps if self.norm is None else self.norm.eps,
-                           residual=residual, out=out)
-        if residual and inplace and y is not x:
-            x.copy_(y)
-            return x
-        return y
+        return ops.transition(xc, self._packed(x.device), row_mask, self.eps if self.norm is None else self.norm.eps,
+                              residual=residual, out=out)
 
     def _forward_gemms(self, x, xc, mask, residual: bool, inplace: bool) -> torch.Tensor:
         if mask is not None:

@@ -86,6 +86,7 @@ class TriangleAttention(nn.Module):
                                      attention_type=AttentionType.TRIANGLE)
         self._pack = None
         self._pack_state = None
+        self._zero_bias = None
 
     def _packed(self, device) -> torch.Tensor:
         """Packed weights for the stand-alone path (no LayerNorm, zero triangle-bias rows)."""
@@ -111,7 +112,10 @@ class TriangleAttention(nn.Module):
         packed = self._packed(x.device)
         lengths = mask_to_lengths(mask_bias, B, R).contiguous()
         if triangle_bias is None:
-            bias2 = torch.zeros((B, ops.HEADS, S, ops.pad8(S)), dtype=torch.bfloat16, device=x.device)
+            key = (B, S, x.device)
+            if self._zero_bias is None or self._zero_bias[0] != key:  # kept per shape: no allocation per call
+                self._zero_bias = (key, torch.zeros((B, ops.HEADS, S, ops.pad8(S)), dtype=torch.bfloat16, device=x.device))
+            bias2 = self._zero_bias[1]
         else:
             pad = -triangle_bias.shape[-1] % 8
             tb = torch.nn.functional.pad(triangle_bias, (0, pad)) if pad else triangle_bias
@@ -247,6 +251,8 @@ class TriangleAttentionNode(nn.Module):
         bias = ensure_buffer(buffers, "tri_attn_bias", (B, ops.HEADS, S, ops.pad8(S)), torch.bfloat16, x.device)
         if self.transposed_bias and bias is None:
             bias = torch.zeros((B, ops.HEADS, S, ops.pad8(S)), dtype=torch.bfloat16, device=x.device)
+        elif self.transposed_bias and ops.pad8(S) != S:
+            bias[..., S:].zero_()  # the transposed write covers keys < S only: keep the key padding of a caller's buffer defined
         # xk is already in kernel order, so the prologue is always called in its "starting" form here
         if chunked:
             # the bias of every row is needed before any row can attend: one bias-only pass first

@@ -159,26 +159,50 @@ def node_forward(z: torch.Tensor, mask: torch.Tensor | None, w: NodeWeights, nod
     return out.transpose(1, 2) if node_type == ENDING else out
 
 
+def triangle_bias(z: torch.Tensor, w: NodeWeights, node_type: int, *, eps: float = 1e-5, slab: int = 128) -> torch.Tensor:
+    """The triangle bias ``[B, H, q, k]`` of every pair row, computed ``slab`` rows at a time so that a 4096-token
+    tensor never needs a full-size fp32 temporary.  Same LayerNorm + projection as ``node_stages``
+    (bionemo_ir/_torch/layers/triangle_nodes.py:252-265)."""
+    dtype = w.ln_w.dtype
+    xt = z.transpose(1, 2) if node_type == ENDING else z
+    B, R, S, c = xt.shape
+    tb = torch.empty(B, w.w_bias.shape[0], R, S, dtype=dtype, device=z.device)
+    for r0 in range(0, R, slab):
+        normed = F.layer_norm(xt[:, r0:r0 + slab].to(dtype), (c,), w.ln_w, w.ln_b, eps)
+        tb[:, :, r0:r0 + slab] = F.linear(normed, w.w_bias).permute(0, 3, 1, 2)
+    return tb
+
+
 def node_forward_rows(z: torch.Tensor, mask: torch.Tensor | None, w: NodeWeights, node_type: int, rows: torch.Tensor,
-                      *, residual: bool = False, heads: int = 4, inf: float = 1e9, eps: float = 1e-5) -> torch.Tensor:
+                      *, residual: bool = False, heads: int = 4, inf: float = 1e9, eps: float = 1e-5,
+                      tri_bias: torch.Tensor | None = None) -> torch.Tensor:
     """``node_forward`` restricted to the pair rows ``rows`` of the node's own row axis (second pair axis of ``z``
     for the ending node): returns ``[B, len(rows), S, c]`` in kernel order.
 
     A row's attention needs only that row of q/k/v/g plus the triangle bias of *all* rows, so sampled rows are exact
-    and cheap; large shapes are checked and timed through this function.  Same reference lines as ``node_stages``.
+    and cheap; large shapes are checked and timed through this function.  ``tri_bias`` takes the bias of all rows
+    from an earlier ``triangle_bias`` call (then only the sampled rows are normalised here); ``mask`` may then be
+    given for the sampled rows only, ``[B, len(rows), S]`` in kernel order.  Same reference lines as ``node_stages``.
     """
     dtype = w.ln_w.dtype
-    x = z.to(dtype)
-    xt = x.transpose(1, 2) if node_type == ENDING else x
+    xt = z.transpose(1, 2) if node_type == ENDING else z
     B, R, S, c = xt.shape
     d = w.w_in.shape[0] // (4 * heads)
-    normed = F.layer_norm(xt, (c,), w.ln_w, w.ln_b, eps)
-    tb = F.linear(normed, w.w_bias).permute(0, 3, 1, 2)  # [B, H, q, k] from every row
+    if tri_bias is None:
+        xt = xt.to(dtype)
+        normed = F.layer_norm(xt, (c,), w.ln_w, w.ln_b, eps)
+        tb = F.linear(normed, w.w_bias).permute(0, 3, 1, 2)  # [B, H, q, k] from every row
+        n_s, x_s = normed[:, rows], xt[:, rows]
+    else:
+        tb = tri_bias
+        x_s = xt[:, rows].to(dtype)
+        n_s = F.layer_norm(x_s, (c,), w.ln_w, w.ln_b, eps)
     if mask is None:
-        mask = xt.new_ones(B, R, S)
-    elif node_type == ENDING:
-        mask = mask.transpose(1, 2)
-    n_s, m_s, x_s = normed[:, rows], mask[:, rows], xt[:, rows]
+        m_s = x_s.new_ones(B, len(rows), S)
+    elif mask.shape[1] == len(rows) and mask.shape[1] != R:
+        m_s = mask
+    else:
+        m_s = (mask.transpose(1, 2) if node_type == ENDING else mask)[:, rows]
     r = n_s.shape[1]
     proj = F.linear(n_s, w.w_in, w.b_in)
     q, k, v, g = proj.split(heads * d, dim=-1)

@@ -37,6 +37,26 @@ def test_pipelined_batches_equal_serial_calls():
             assert torch.equal(got, ref)
 
 
+def test_function_that_updates_its_slot_in_place():
+    """``fn`` may return the slot tensor itself: the next copy into the slot must wait for the copy-out too."""
+    import bionemo_inference_runtime_b200 as b200
+
+    torch.manual_seed(18)
+    n = 128
+    node = build_node(bf16_weights(orc.make_node_weights(43)), orc.STARTING)
+    bufs = [{}, {}, {}]
+
+    def step(z, slot):
+        return node(z, buffers=bufs[slot], residual=True, inplace_residual=True)  # returns z (the slot)
+
+    inputs = [torch.randn(1, n, n, 128).bfloat16().pin_memory() for _ in range(9)]
+    outputs = [torch.empty_like(t).pin_memory() for t in inputs]
+    want = [step(t.to(DEV), 2).cpu() for t in inputs]
+    b200.HostPipeline(step, inputs[0], DEV, depth=2).run(inputs, outputs)
+    for got, ref in zip(outputs, want):
+        assert torch.equal(got, ref)
+
+
 def test_pipeline_rejects_pageable_or_mismatched_tensors():
     import bionemo_inference_runtime_b200 as b200
 

@@ -324,6 +324,23 @@ def test_transition_large_mean_rows_and_determinism():
     assert torch.equal(upd, t(x))
 
 
+def test_transition_on_a_transposed_view_runs_in_storage_order():
+    """A permuted view is processed without a copy; ``inplace`` writes the caller's storage; slices are refused."""
+    torch.manual_seed(24)
+    w = bf16_weights(orc.make_transition_weights(24, identity_ln=False))
+    t = build_transition(w)
+    x = torch.randn(2, 40, 56, 128).bfloat16().to(DEV)
+    mask = (torch.rand(2, 56, 40, device=DEV) > 0.3).float()
+    view = x.transpose(1, 2)  # [2, 56, 40, 128], not contiguous
+    want = t(view.contiguous(), mask, residual=True)
+    assert torch.equal(t(view, mask, residual=True), want)
+    xc = x.clone()
+    got = t(xc.transpose(1, 2), mask, residual=True, inplace=True)
+    assert got.data_ptr() == xc.data_ptr() and torch.equal(xc.transpose(1, 2), want)
+    with pytest.raises(ValueError, match="permuted view"):
+        t(x[:, ::2])
+
+
 def test_transition_without_norm():
     torch.manual_seed(10)
     w = bf16_weights(orc.make_transition_weights(23))
