@@ -17,15 +17,15 @@
 //   tcgen05  O += P·V           (128x32x128: P is the A operand from TMEM, V the MN-major B operand from
 //                                its [key][d] tile); O is only rescaled when a tile's sum would leave the
 //                                safe fp32 range
-// The two 128-query halves are handled by two softmax warpgroups that share K/V and alternate on the
-// tensor core.  The MMA warp runs one key tile ahead (also across work items), so the next scores are
-// in TMEM before a warpgroup asks for them.
+// The two 128-query halves are handled by two softmax warpgroups that share K/V.  Each half has its own
+// score-MMA warp, which runs one key tile ahead (also across work items), so the next scores are in TMEM
+// before a warpgroup asks for them.
 //
 // A pair row without a valid key takes a constant path in "uniform" mode (probabilities all 1: the output is the
 // mean of V, as the eager reference computes it) and is skipped in "zeros" mode.
 //
 // Warp roles (384 threads): warps 0-3 softmax half 0, warps 4-7 softmax half 1, warp 8 TMA producer,
-// warp 9 score-MMA issuer / TMEM owner, warp 10 P·V-MMA issuer, warp 11 idle.  The third warpgroup gives most
+// warps 9 and 11 score-MMA issuers of the two halves (warp 9 owns TMEM), warp 10 P·V-MMA issuer.  The third warpgroup gives most
 // of its registers to the softmax warpgroups (setmaxnreg).
 #include "common.cuh"
 #include "layout.h"
@@ -110,21 +110,24 @@ __device__ __forceinline__ int fast_div(int n, uint32_t mul, uint32_t shr) {
 // Row length of a work item as stored (not clamped yet).
 __device__ __forceinline__ int item_raw_length(const AttnParams& p, int item) {
   if (p.lengths == nullptr) return p.S;
-  const int t = fast_div(item, p.r_mul, p.r_shr);
-  const int r = item - t * p.R;
-  const int b = fast_div(t, p.qp_mul, p.qp_shr) / kHeads;
+  const int t = fast_div(item, p.qp_mul, p.qp_shr);
+  const int t2 = fast_div(t, p.r_mul, p.r_shr);
+  const int r = t - t2 * p.R;
+  const int b = t2 / kHeads;
   return p.lengths[b * p.ls_b + r * p.ls_r];
 }
 
 __device__ __forceinline__ Item decode_item(const AttnParams& p, int item, int len) {
   Item it;
-  int t = fast_div(item, p.r_mul, p.r_shr);
-  it.r = item - t * p.R;
-  const int t2 = fast_div(t, p.qp_mul, p.qp_shr);
-  const int qp = t - t2 * p.q_pairs;
-  t = t2;
-  it.h = t % kHeads;
-  it.b = t / kHeads;
+  // Items are ordered (b, h, r, query pair) with the query pair fastest: the CTAs that run at the same time work
+  // on the query tiles of neighbouring pair rows, so a row's K and V come from HBM once (and then from L2) while
+  // the head's bias, shared by all rows, stays in L2.
+  const int t = fast_div(item, p.qp_mul, p.qp_shr);
+  const int qp = item - t * p.q_pairs;
+  const int t2 = fast_div(t, p.r_mul, p.r_shr);
+  it.r = t - t2 * p.R;
+  it.h = t2 % kHeads;
+  it.b = t2 / kHeads;
   it.q0 = qp * 2 * kQTile;
   it.br = it.b * p.R + it.r;
   len = len < 0 ? 0 : (len > p.S ? p.S : len);
@@ -193,9 +196,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     abort_flag[1] = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + (Q_FULL + i) * 8, 1);
-      mbar_init(bars + (Q_EMPTY + i) * 8, 1);
+      mbar_init(bars + (Q_EMPTY + i) * 8, 2);   // one arrival per score-MMA warp
       mbar_init(bars + (KB_FULL + i) * 8, 1);
-      mbar_init(bars + (KB_EMPTY + i) * 8, 1);
+      mbar_init(bars + (KB_EMPTY + i) * 8, 2);  // one arrival per score-MMA warp
       mbar_init(bars + (S_FULL + i) * 8, 1);
       mbar_init(bars + (S_FREE + i) * 8, 4);
       mbar_init(bars + (P_FULL + i) * 8, 4);
@@ -289,16 +292,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         mbar_wait(bars + (V_FULL + last % kVStages) * 8, (last / kVStages) & 1, abort_flag + 1);
       }
     }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ score MMA issuer (S = Q·Kᵀ + I·Bias)
-    // Runs one key tile ahead of the softmax (also across work items): the only thing it waits for besides
-    // the loads is that a half's S buffer has been read out.
+  } else if (warp == 9 || warp == 11) {
+    // ------------------------------------------------------------------ score MMA issuers (S = Q·Kᵀ + I·Bias)
+    // One warp per 128-query half (a single thread issues a tcgen05.mma about every 80 clocks, so the ten MMAs
+    // of a half per key tile are issued side by side).  Each runs one key tile ahead of the softmax (also across
+    // work items): the only thing it waits for besides the loads is that its half's S buffer has been read out.
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kQTile, kKTile);                // Q·Kᵀ: both operands K-major
       constexpr uint32_t idesc_b1 = make_idesc_bf16(kQTile, 128, false, true);     // I·Bias: B MN-major
+      const int w = warp == 9 ? 0 : 1;
       const uint32_t ti = tmem_base + kTmemI;
-      const uint32_t d0 = tmem_base + kTmemS;  // S of half 0; half 1 follows 128 columns later
-      int n0 = 0, n1 = 0;                      // S tiles issued per half (phase of S_FREE)
+      const uint32_t d = tmem_base + kTmemS + w * 128;  // S of this half
+      int n = 0;                                        // S tiles issued (phase of S_FREE)
       bool ok = true;
       TileCursor c;
       cursor_init(p, c, my_items);
@@ -308,36 +313,34 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (c.kt == 0) ok = mbar_wait(bars + (Q_FULL + ib) * 8, (c.qi >> 1) & 1, abort_flag);
         ok = ok && mbar_wait(bars + (KB_FULL + stage) * 8, (c.g / kStages) & 1, abort_flag);
         if (!ok) break;
-        // One descriptor per operand tile; the K steps only add a constant to its address field (in 16-byte
-        // units), which keeps this single-thread issue path down to a few instructions per MMA.
-        const uint32_t sbase = base + kSmStage + stage * kStageBytes;
-        const uint64_t dk = make_smem_desc(sbase, 16, 512, kLayoutSw64);
-        const uint64_t dq0 = make_smem_desc(base + kSmQ + ib * 16384, 16, 512, kLayoutSw64);
-        // Bias tiles: [128 query rows][64 keys] blocks with 128-byte swizzle, 16 KiB apart: keys 0-63 and
-        // 64-127 of half 0, then of half 1.  As B[key][query] this is MN-major with 16 query rows (2 KiB)
-        // per K step.
-        const uint64_t db0 = make_smem_desc(sbase + 8192, 16384, 1024, kLayoutSw128);
-        // The halves are issued separately, each as soon as its own S buffer has been read out, so the two
-        // softmax warpgroups need not run in step.
-        for (int w = 0; w < it.nvalid; ++w) {
-          ok = mbar_wait(bars + (S_FREE + w) * 8, ((w ? n1 : n0) & 1) ^ 1, abort_flag);
+        if (w < it.nvalid) {
+          // One descriptor per operand tile; the K steps only add a constant to its address field (in 16-byte
+          // units), which keeps this single-thread issue path down to a few instructions per MMA.
+          const uint32_t sbase = base + kSmStage + stage * kStageBytes;
+          const uint64_t dk = make_smem_desc(sbase, 16, 512, kLayoutSw64);
+          const uint64_t dq = make_smem_desc(base + kSmQ + ib * 16384 + w * 8192, 16, 512, kLayoutSw64);
+          // Bias tiles: [128 query rows][64 keys] blocks with 128-byte swizzle, 16 KiB apart: keys 0-63 and
+          // 64-127 of half 0, then of half 1.  As B[key][query] this is MN-major with 16 query rows (2 KiB)
+          // per K step.
+          const uint64_t db = make_smem_desc(sbase + 8192 + w * 32768, 16384, 1024, kLayoutSw128);
+          ok = mbar_wait(bars + (S_FREE + w) * 8, (n & 1) ^ 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t d = d0 + w * 128;
-          const uint64_t dq = dq0 + w * 512;  // Q of half 1 lies 8 KiB further
           if (!it.uniform) {  // a row without a valid key has equal logits: the softmax warps need no scores
             umma_ss(d, dq, dk, idesc_s, 0u);
             umma_ss(d, dq + 2, dk + 2, idesc_s, 1u);  // second 16 channels: +32 bytes
-            const uint64_t db = db0 + w * 2048;  // bias of half 1 lies 32 KiB further
 #pragma unroll
             for (int j = 0; j < 8; ++j) umma_ts(d, ti + j * 8, db + j * 128, idesc_b1, 1u);
           }
           umma_commit(bars + (S_FULL + w) * 8);
-          if (w) ++n1; else ++n0;
+          ++n;
+          umma_commit(bars + (KB_EMPTY + stage) * 8);                      // K and bias are free once both halves' MMAs ran
+          if (c.kt == it.nkt - 1) umma_commit(bars + (Q_EMPTY + ib) * 8);  // last use of this item's Q
+        } else {
+          // this half holds no query of the item: only keep the shared barriers' counts complete
+          mbar_arrive(bars + (KB_EMPTY + stage) * 8);
+          if (c.kt == it.nkt - 1) mbar_arrive(bars + (Q_EMPTY + ib) * 8);
         }
-        if (!ok) break;
-        umma_commit(bars + (KB_EMPTY + stage) * 8);                      // K and bias are free once these MMAs ran
-        if (c.kt == it.nkt - 1) umma_commit(bars + (Q_EMPTY + ib) * 8);  // last use of this item's Q
         cursor_next(p, c, my_items);
       }
     }
