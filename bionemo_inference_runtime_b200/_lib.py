@@ -36,6 +36,7 @@ SIGNATURES: dict[str, tuple] = {
     "b200ta_transition_pack_bytes": (c_size_t, []),
     "b200ta_pack_node_weights": (c_int, [c_void_p] * 7 + [c_int, c_void_p, c_void_p]),
     "b200ta_pack_transition_weights": (c_int, [c_void_p] * 4 + [c_int, c_void_p, c_void_p]),
+    "b200ta_pack_relu_transition_weights": (c_int, [c_void_p] * 6 + [c_int, c_void_p, c_void_p]),
     "b200ta_prologue": (
         c_int,
         [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int,
@@ -65,6 +66,10 @@ SIGNATURES: dict[str, tuple] = {
          c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
     ),
     "b200ta_transition": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p],
+    ),
+    "b200ta_transition_relu": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p],
     ),

@@ -188,6 +188,31 @@ int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const voi
                                              reinterpret_cast<int*>(base + kTransFlagsOff));
   convert_kernel<<<(kC * kHidden + 255) / 256, 256, 0, s>>>(w2, weight_dtype, size_t(kC) * kHidden,
                                                             reinterpret_cast<__nv_bfloat16*>(base + kTransW2Off), nullptr);
+  convert_kernel<<<1, kC, 0, s>>>(nullptr, weight_dtype, kC, nullptr, reinterpret_cast<float*>(base + kTransB2Off));
+  B200TA_CHECK_CUDA(cudaGetLastError());
+  return B200TA_OK;
+}
+
+int b200ta_pack_relu_transition_weights(const void* ln_w, const void* ln_b, const void* w1, const void* b1,
+                                        const void* w2, const void* b2, int weight_dtype, void* packed,
+                                        void* stream) {
+  using namespace b200ta;
+  B200TA_REQUIRE(w1 && w2 && packed, "pack_relu_transition_weights: NULL pointer");
+  B200TA_REQUIRE((ln_w == nullptr) == (ln_b == nullptr), "pack_relu_transition_weights: pass both LayerNorm vectors or neither");
+  B200TA_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 255u) == 0, "pack_relu_transition_weights: packed must be 256-byte aligned");
+  int rc = check_dtype(weight_dtype);
+  if (rc != B200TA_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* base = static_cast<char*>(packed);
+  // the 512 hidden rows (with the first linear's bias in their constant term) take the value half; the gate half
+  // is zero and unused by the ReLU form of the kernel
+  fold_rows_kernel<<<kTransRows, kC, 0, s>>>(w1, kHidden, nullptr, 0, b1, ln_w, ln_b, weight_dtype, 0, 0, 1.f,
+                                             reinterpret_cast<__nv_bfloat16*>(base + kTransW1Off),
+                                             reinterpret_cast<float2*>(base + kTransScOff),
+                                             reinterpret_cast<int*>(base + kTransFlagsOff));
+  convert_kernel<<<(kC * kHidden + 255) / 256, 256, 0, s>>>(w2, weight_dtype, size_t(kC) * kHidden,
+                                                            reinterpret_cast<__nv_bfloat16*>(base + kTransW2Off), nullptr);
+  convert_kernel<<<1, kC, 0, s>>>(b2, weight_dtype, kC, nullptr, reinterpret_cast<float*>(base + kTransB2Off));
   B200TA_CHECK_CUDA(cudaGetLastError());
   return B200TA_OK;
 }

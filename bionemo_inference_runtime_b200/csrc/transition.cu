@@ -1,5 +1,7 @@
 // Pair transition for sm_100a: out = [x +] mask * ( (silu(gate) * value) · W2ᵀ ),
 // [value|gate] = LayerNorm(x) · W1ᵀ, hidden 512, one kernel, hidden kept on chip.
+// The ReLU form (kRelu) computes out = [x +] mask * ( relu(LayerNorm(x) · W1ᵀ + b1) · W2ᵀ + b2 ) with the same
+// pipeline: its 512 hidden rows sit in the value half of the packed first linear, the gate half is zero.
 //
 // A persistent CTA per SM walks 128-row tiles of x.  The hidden dimension is cut in
 // 8 chunks of 64 units; for each chunk
@@ -29,6 +31,7 @@ struct TransParams {
   int num_tiles;
   const float2* sc;  // [1024] {rowsum, const} of the folded W1 rows
   const int* flags;  // flags[0] != 0 -> apply LayerNorm statistics
+  const float* b2;   // [128] bias of the second linear (ReLU form)
   const __nv_bfloat16* mask;
   float eps;
   int add_residual;
@@ -65,6 +68,7 @@ enum Bar {
 
 constexpr uint32_t kTmemAcc1 = 0, kTmemAcc2 = 256, kTmemCols = 512;
 
+template <bool kRelu>
 __global__ void __launch_bounds__(kThreads, 1)
 transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w1,
                   const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ OutMaps tm_outs,
@@ -102,6 +106,10 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   for (int q = threadIdx.x; q < kHidden; q += kThreads) {  // 256 value pairs, then 256 gate pairs
     const float2 a = p.sc[2 * q], b = p.sc[2 * q + 1];
     reinterpret_cast<float4*>(gen + kSmSc)[q] = make_float4(a.x, b.x, a.y, b.y);
+  }
+  if (kRelu) {  // the gate half of the constants is unused by the ReLU form: the output bias takes its place
+    __syncthreads();
+    if (threadIdx.x < kC) reinterpret_cast<float*>(gen + kSmSc + 4096)[threadIdx.x] = p.b2[threadIdx.x];
   }
   if (warp == 9) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
   tc_fence_before();
@@ -274,14 +282,19 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const float4 cv = scv[qt * 8 + t], cg = scg[qt * 8 + t];
             const uint64_t val2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xv[2 * t]), __uint_as_float(xv[2 * t + 1])),
                                             fma_f32x2(nmr2, pack_f32x2(cv.x, cv.y), pack_f32x2(cv.z, cv.w)));
-            const uint64_t h2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xg[2 * t]), __uint_as_float(xg[2 * t + 1])),
-                                          fma_f32x2(nmr2, pack_f32x2(cg.x, cg.y), pack_f32x2(cg.z, cg.w)));  // gate / 2
-            float h0, h1;
-            unpack_f32x2(h2, h0, h1);
-            // silu(gate) * value = (h * tanh(h) + h) * value
-            const uint64_t hid2 = mul_f32x2(fma_f32x2(h2, pack_f32x2(tanh_approx(h0), tanh_approx(h1)), h2), val2);
             float o0, o1;
-            unpack_f32x2(hid2, o0, o1);
+            if (kRelu) {
+              unpack_f32x2(val2, o0, o1);
+              o0 = fmaxf(o0, 0.f), o1 = fmaxf(o1, 0.f);
+            } else {
+              const uint64_t h2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xg[2 * t]), __uint_as_float(xg[2 * t + 1])),
+                                            fma_f32x2(nmr2, pack_f32x2(cg.x, cg.y), pack_f32x2(cg.z, cg.w)));  // gate / 2
+              float h0, h1;
+              unpack_f32x2(h2, h0, h1);
+              // silu(gate) * value = (h * tanh(h) + h) * value
+              const uint64_t hid2 = mul_f32x2(fma_f32x2(h2, pack_f32x2(tanh_approx(h0), tanh_approx(h1)), h2), val2);
+              unpack_f32x2(hid2, o0, o1);
+            }
             pk[t] = pack_bf16x2(o0, o1);
           }
 #pragma unroll
@@ -322,10 +335,18 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           for (int t = 0; t < 16; ++t) res[t] = 0u;
         }
         uint32_t pk[16];
+        if (kRelu) {
+          const float* b2s = reinterpret_cast<const float*>(gen + kSmSc + 4096) + e * 64 + g * 32;
 #pragma unroll
-        for (int t = 0; t < 16; ++t)
-          pk[t] = pack_bf16x2(fmaf(mk, __uint_as_float(a[2 * t]), bf16_lo(res[t])),
-                              fmaf(mk, __uint_as_float(a[2 * t + 1]), bf16_hi(res[t])));
+          for (int t = 0; t < 16; ++t)
+            pk[t] = pack_bf16x2(fmaf(mk, __uint_as_float(a[2 * t]) + b2s[2 * t], bf16_lo(res[t])),
+                                fmaf(mk, __uint_as_float(a[2 * t + 1]) + b2s[2 * t + 1], bf16_hi(res[t])));
+        } else {
+#pragma unroll
+          for (int t = 0; t < 16; ++t)
+            pk[t] = pack_bf16x2(fmaf(mk, __uint_as_float(a[2 * t]), bf16_lo(res[t])),
+                                fmaf(mk, __uint_as_float(a[2 * t + 1]), bf16_hi(res[t])));
+        }
         if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
 #pragma unroll
@@ -377,7 +398,7 @@ namespace {
 // outs[0..num_outs): the output (plain form, one entry, row stride os) or every GPU's row shard (scatter form).
 int launch_transition(const void* x, int64_t xs, const void* mask, const void* packed, float eps, void* const* outs,
                       int num_outs, int64_t os, int64_t rows, int add_residual, int num_peers, int cols, int tokens,
-                      int col0, void* stream) {
+                      int col0, void* stream, bool relu = false) {
   B200TA_REQUIRE(x && packed && outs, "transition: NULL pointer");
   B200TA_REQUIRE(rows > 0 && rows < (int64_t(1) << 31), "transition: rows=%lld out of range", (long long)rows);
   B200TA_REQUIRE(xs >= kC && xs % 8 == 0 && os >= kC && os % 8 == 0, "transition: row strides must be >= 128 and multiples of 8 elements");
@@ -424,15 +445,21 @@ int launch_transition(const void* x, int64_t xs, const void* mask, const void* p
   p.num_tiles = int((rows + kTileM - 1) / kTileM);
   p.sc = reinterpret_cast<const float2*>(pk + kTransScOff);
   p.flags = reinterpret_cast<const int*>(pk + kTransFlagsOff);
+  p.b2 = reinterpret_cast<const float*>(pk + kTransB2Off);
   p.mask = static_cast<const __nv_bfloat16*>(mask);
   p.eps = eps;
   p.add_residual = add_residual ? 1 : 0;
   p.status = st->status_dev;
   p.num_peers = num_peers, p.cols = cols, p.tokens = tokens, p.col0 = col0;
 
-  B200TA_CHECK_CUDA(cudaFuncSetAttribute(transition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmDynamic));
   const int grid = p.num_tiles < st->num_sms ? p.num_tiles : st->num_sms;
-  transition_kernel<<<grid, kThreads, kSmDynamic, static_cast<cudaStream_t>(stream)>>>(tm_x, tm_w1, tm_w2, tm_outs, p);
+  if (relu) {
+    B200TA_CHECK_CUDA(cudaFuncSetAttribute(transition_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmDynamic));
+    transition_kernel<true><<<grid, kThreads, kSmDynamic, static_cast<cudaStream_t>(stream)>>>(tm_x, tm_w1, tm_w2, tm_outs, p);
+  } else {
+    B200TA_CHECK_CUDA(cudaFuncSetAttribute(transition_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmDynamic));
+    transition_kernel<false><<<grid, kThreads, kSmDynamic, static_cast<cudaStream_t>(stream)>>>(tm_x, tm_w1, tm_w2, tm_outs, p);
+  }
   B200TA_CHECK_CUDA(cudaGetLastError());
   return B200TA_OK;
 }
@@ -445,6 +472,11 @@ extern "C" {
 int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* packed, float eps, void* out,
                       int64_t os, int64_t rows, int add_residual, void* stream) {
   return b200ta::launch_transition(x, xs, mask, packed, eps, &out, 1, os, rows, add_residual, 0, 0, 0, 0, stream);
+}
+
+int b200ta_transition_relu(const void* x, int64_t xs, const void* mask, const void* packed, float eps, void* out,
+                           int64_t os, int64_t rows, int add_residual, void* stream) {
+  return b200ta::launch_transition(x, xs, mask, packed, eps, &out, 1, os, rows, add_residual, 0, 0, 0, 0, stream, true);
 }
 
 int b200ta_transition_scatter(const void* x, const void* mask, const void* packed, float eps, void* const* peer_out,

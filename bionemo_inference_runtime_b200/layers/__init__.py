@@ -11,7 +11,7 @@ from .buffers import PreallocatedBuffers, ensure_buffer
 from .linear import Linear, WeightMode, WeightsLoadingConfig
 from .pairformer import (PairformerLayerV1, PairformerLayerV2, PairformerModule, PairformerNoSeqLayer,
                          PairformerNoSeqModule)
-from .transition import Transition
+from .transition import PairTransition, Transition
 from .triangle_multiplication import (TriangleMultiplicationMetadata, TriangleMultiplicationNode,
                                       TriangleMultiplicationNodeType, precompute_trimul_metadata,
                                       set_trimul_token_padding)
@@ -23,7 +23,7 @@ __all__ = [
     "create_attention", "get_attention_backend", "mask_to_lengths", "precompute_pair_masks",
     "register_precompute_pair_masks", "CHUNK_REGISTRY", "PAIR_TRANSITION", "TRIANGLE_ATTENTION", "ChunkPolicy",
     "chunk_apply", "default_autochunk_min", "iter_chunks", "PreallocatedBuffers", "ensure_buffer", "Linear",
-    "WeightMode", "WeightsLoadingConfig", "Transition", "TriangleAttention", "TriangleAttentionEndingNode",
+    "WeightMode", "WeightsLoadingConfig", "Transition", "PairTransition", "TriangleAttention", "TriangleAttentionEndingNode",
     "TriangleAttentionNode", "TriangleAttentionNodeType", "TriangleAttentionStartingNode", "split_pair_bias_proj",
     "TriangleMultiplicationMetadata", "TriangleMultiplicationNode", "TriangleMultiplicationNodeType",
     "precompute_trimul_metadata", "set_trimul_token_padding", "PairformerNoSeqLayer", "PairformerNoSeqModule",

@@ -152,3 +152,70 @@ class Transition(nn.Module):
             x.copy_(y)
             return x
         return y
+
+
+class PairTransition(nn.Module):
+    """ReLU pair transition ``linear_2(relu(linear_1(LayerNorm(z))))`` over ``[*, N, N, c_z]``, both linears with
+    biases, on the fused sm_100a kernel (``b200ta_transition_relu``).
+
+    Drop-in counterpart of ``PairTransition`` (``bionemo_ir/_torch/layers/transition.py:591-656``, body
+    ``_ReluTransition`` l.540-588): same constructor, ``forward(z, mask=None, *, residual=False)`` and
+    ``state_dict`` keys (``layer_norm.{weight,bias}``, ``linear_1.{weight,bias}`` ``[n*c_z, c_z]``,
+    ``linear_2.{weight,bias}`` ``[c_z, n*c_z]``).  The kernel is specialised for ``c_z = 128`` and ``n = 4``.
+    """
+
+    def __init__(self, c_z: int, n: int, eps: float = 1e-5, dtype: torch.dtype = None, skip_create_weights: bool = False,
+                 auto_chunk_policy: ChunkPolicy | None = None):
+        super().__init__()
+        if (c_z, n * c_z) != (ops.C, ops.HIDDEN):
+            raise ValueError(f"the sm_100a ReLU transition kernel takes c_z={ops.C}, n={ops.HIDDEN // ops.C}; got c_z={c_z}, n={n}")
+        self.c_z, self.n, self.dtype = c_z, n, dtype
+        self.auto_chunk_policy = auto_chunk_policy  # accepted; the fused kernel holds no activation beyond its output
+        self.layer_norm = nn.LayerNorm(c_z, eps=eps, dtype=dtype)
+        self.linear_1 = Linear(c_z, n * c_z, bias=True, dtype=dtype, skip_create_weights=skip_create_weights)
+        self.linear_2 = Linear(n * c_z, c_z, bias=True, dtype=dtype, skip_create_weights=skip_create_weights)
+        self._pack = None
+        self._pack_state = None
+        self.register_load_state_dict_post_hook(_refold_after_load_state_dict)
+
+    def _params(self):
+        return (self.layer_norm.weight, self.layer_norm.bias, self.linear_1.weight, self.linear_1.bias,
+                self.linear_2.weight, self.linear_2.bias)
+
+    @torch.no_grad()
+    def post_load_weights(self) -> None:
+        """Refold the LayerNorm-folded weights from the (re)loaded parameters."""
+        if not (self.linear_1._weights_created and self.linear_2._weights_created) or not self.linear_2.weight.is_cuda:
+            self._pack = self._pack_state = None
+            return
+        device = self.linear_2.weight.device  # LayerNorm's parameters may still sit on the host at load time
+        self._pack = ops.pack_relu_transition_weights(*[t.to(device) for t in self._params()])
+        self._pack_state = _weight_state(*self._params())
+
+    def _packed(self, device) -> torch.Tensor:
+        state = _weight_state(*self._params())
+        if self._pack is None or self._pack.device != device or state != self._pack_state:
+            pack = ops.pack_relu_transition_weights(*[t.to(device) for t in self._params()])
+            if not torch.cuda.is_current_stream_capturing():
+                self._pack, self._pack_state = pack, state
+            return pack
+        return self._pack
+
+    def forward(self, z: torch.Tensor, mask: torch.Tensor | None = None, *, residual: bool = False) -> torch.Tensor:
+        """``[z +] mask * (linear_2(relu(linear_1(LayerNorm(z)))))``; ``mask`` holds one value per pair position."""
+        if self.dtype not in (None, torch.bfloat16) or (self.dtype is None and z.dtype != torch.bfloat16):
+            raise ValueError("the sm_100a transition kernel computes in bfloat16; construct the layer with "
+                             "dtype=torch.bfloat16")
+        if not z.is_cuda:
+            raise ValueError("this layer runs on a CUDA device only (no CPU path)")
+        z = z.to(torch.bfloat16)
+        if not z.is_contiguous():
+            order = _storage_order(z)
+            if order is None:
+                raise ValueError("PairTransition takes a contiguous tensor or a permuted view of one (channels last, "
+                                 f"unit stride); got shape {tuple(z.shape)} with strides {z.stride()}")
+            inverse = [order.index(d) for d in range(z.dim())]
+            mask_p = None if mask is None else _row_mask(z, mask).permute(order[:-1])
+            return self.forward(z.permute(order), mask_p, residual=residual).permute(inverse)
+        row_mask = None if mask is None else _row_mask(z, mask)
+        return ops.transition(z, self._packed(z.device), row_mask, self.layer_norm.eps, residual=residual, relu=True)

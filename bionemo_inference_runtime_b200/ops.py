@@ -37,6 +37,10 @@ def _require_cuda_bf16(name: str, t: torch.Tensor) -> None:
 
 
 def _weight_dtype(*tensors: torch.Tensor | None) -> int:
+    """The common dtype code of a set of weights; also refuses host tensors, whose addresses a kernel must never see."""
+    devices = {t.device for t in tensors if t is not None}
+    if len(devices) != 1 or next(iter(devices)).type != "cuda":
+        raise ValueError(f"weights must all live on one CUDA device, got {sorted(map(str, devices))}")
     dtypes = {t.dtype for t in tensors if t is not None}
     if dtypes == {torch.bfloat16}:
         return _lib.DTYPE_BF16
@@ -71,6 +75,17 @@ def pack_transition_weights(ln_w, ln_b, w1, w2) -> torch.Tensor:
     dt = _weight_dtype(*ts)
     packed = torch.empty(_lib.load().b200ta_transition_pack_bytes(), dtype=torch.uint8, device=ts[2].device)
     _lib.call("b200ta_pack_transition_weights", *[_ptr(t) for t in ts], dt, packed.data_ptr(), _stream())
+    return packed
+
+
+def pack_relu_transition_weights(ln_w, ln_b, w1, b1, w2, b2) -> torch.Tensor:
+    """Fold LayerNorm into linear_1 of the ReLU pair transition; returns the opaque packed buffer."""
+    ts = [_contig(t) for t in (ln_w, ln_b, w1, b1, w2, b2)]
+    if tuple(ts[2].shape) != (HIDDEN, C) or tuple(ts[4].shape) != (C, HIDDEN):
+        raise ValueError(f"kernel is specialised for width={C}, hidden={HIDDEN}: got {tuple(ts[2].shape)}, {tuple(ts[4].shape)}")
+    dt = _weight_dtype(*ts)
+    packed = torch.empty(_lib.load().b200ta_transition_pack_bytes(), dtype=torch.uint8, device=ts[2].device)
+    _lib.call("b200ta_pack_relu_transition_weights", *[_ptr(t) for t in ts], dt, packed.data_ptr(), _stream())
     return packed
 
 
@@ -263,8 +278,9 @@ def epilogue(og: torch.Tensor, packed: torch.Tensor, residual: torch.Tensor | No
 
 
 def transition(x: torch.Tensor, packed: torch.Tensor, mask: torch.Tensor | None = None, eps: float = 1e-5, *,
-               residual: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Fused LayerNorm -> SwiGLU MLP (-> mask) (-> + x) over the rows of ``x[..., 128]``."""
+               residual: bool = False, out: torch.Tensor | None = None, relu: bool = False) -> torch.Tensor:
+    """Fused LayerNorm -> SwiGLU MLP (-> mask) (-> + x) over the rows of ``x[..., 128]``; with ``relu`` the ReLU
+    form ``linear_2(relu(linear_1(LayerNorm(x))))`` (``packed`` from :func:`pack_relu_transition_weights`)."""
     _require_cuda_bf16("x", x)
     if x.shape[-1] != C:
         raise ValueError(f"last dimension must be {C}")
@@ -277,8 +293,8 @@ def transition(x: torch.Tensor, packed: torch.Tensor, mask: torch.Tensor | None 
         raise ValueError("out must be contiguous and shaped like x")
     if mask is not None:
         mask = mask.to(torch.bfloat16).expand(x.shape[:-1]).contiguous()
-    _lib.call("b200ta_transition", x2.data_ptr(), C, _ptr(mask), packed.data_ptr(), float(eps), out.data_ptr(), C,
-              x2.shape[0], 1 if residual else 0, _stream())
+    _lib.call("b200ta_transition_relu" if relu else "b200ta_transition", x2.data_ptr(), C, _ptr(mask), packed.data_ptr(),
+              float(eps), out.data_ptr(), C, x2.shape[0], 1 if residual else 0, _stream())
     return out
 
 

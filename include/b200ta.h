@@ -94,6 +94,16 @@ int b200ta_pack_node_weights(const void* ln_w, const void* ln_b, const void* w_i
 int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const void* w1,
                                    const void* w2, int weight_dtype, void* packed, void* stream);
 
+/*
+ * The ReLU pair transition's weights into a buffer of b200ta_transition_pack_bytes() bytes (for
+ * b200ta_transition_relu).  ln_w, ln_b: [128] or both NULL.  w1: [512,128], b1: [512] or NULL (linear_1).
+ * w2: [128,512], b2: [128] or NULL (linear_2).
+ * Replaces: pack_weights(..., activation="relu"), bionemo_ir/_torch/custom_ops/transition_mlp_w_norm/ops.py:198-302.
+ */
+int b200ta_pack_relu_transition_weights(const void* ln_w, const void* ln_b, const void* w1, const void* b1,
+                                        const void* w2, const void* b2, int weight_dtype, void* packed,
+                                        void* stream);
+
 /* ---- triangle-attention node ------------------------------------------------- */
 
 /*
@@ -249,6 +259,16 @@ int b200ta_node_forward_static(const void* z, int64_t zs_b, int64_t zs_r, int64_
  */
 int b200ta_transition(const void* x, int64_t xs, const void* mask, const void* packed, float eps,
                       void* out, int64_t os, int64_t rows, int add_residual, void* stream);
+
+/*
+ * The ReLU pair transition  out = [x +] mask * ( relu(LayerNorm(x) · W1ᵀ + b1) · W2ᵀ + b2 )  (hidden 512, both
+ * linears with biases), on the same kernel pipeline; arguments as for b200ta_transition, `packed` from
+ * b200ta_pack_relu_transition_weights.
+ * Replaces: PairTransition / _ReluTransition (bionemo_ir/_torch/layers/transition.py:540-656) and its fused form
+ * transition_mlp_w_norm(..., activation="relu") (bionemo_ir/_torch/custom_ops/transition_mlp_w_norm/ops.py:198-338).
+ */
+int b200ta_transition_relu(const void* x, int64_t xs, const void* mask, const void* packed, float eps, void* out,
+                           int64_t os, int64_t rows, int add_residual, void* stream);
 
 /*
  * The transition of a column shard x = [B][tokens][cols][128] (contiguous bf16, cols = tokens / num_peers, a

@@ -268,6 +268,46 @@ def transition_forward(x: torch.Tensor, mask: torch.Tensor | None, w: Transition
     return xd + y if residual else y
 
 
+@dataclass
+class ReluTransitionWeights:
+    """Parameters of the ReLU pair transition, named as in the reference state_dict."""
+
+    ln_w: torch.Tensor  # layer_norm.weight [c]
+    ln_b: torch.Tensor  # layer_norm.bias [c]
+    w1: torch.Tensor  # linear_1.weight [n*c, c]
+    b1: torch.Tensor  # linear_1.bias [n*c]
+    w2: torch.Tensor  # linear_2.weight [c, n*c]
+    b2: torch.Tensor  # linear_2.bias [c]
+
+    def to(self, dtype: torch.dtype) -> "ReluTransitionWeights":
+        return ReluTransitionWeights(*[t.to(dtype) for t in self.__dict__.values()])
+
+
+def make_relu_transition_weights(seed: int, c: int = 128, n: int = 4, std: float = 0.05) -> ReluTransitionWeights:
+    g = torch.Generator().manual_seed(seed)
+    return ReluTransitionWeights(1 + 0.2 * torch.randn(c, generator=g), 0.2 * torch.randn(c, generator=g),
+                                 torch.randn(n * c, c, generator=g) * std, 0.1 * torch.randn(n * c, generator=g),
+                                 torch.randn(c, n * c, generator=g) * std, 0.1 * torch.randn(c, generator=g))
+
+
+def relu_transition_forward(z: torch.Tensor, mask: torch.Tensor | None, w: ReluTransitionWeights, *,
+                            residual: bool = False, eps: float = 1e-5) -> torch.Tensor:
+    """``[z +] mask * linear_2(relu(linear_1(LayerNorm(z))))``, both linears with biases.
+
+    Reference: PairTransition._forward_impl (bionemo_ir/_torch/layers/transition.py:631-656) and
+    transition_mlp_w_norm_reference with activation="relu"
+    (bionemo_ir/_torch/custom_ops/transition_mlp_w_norm/ops.py:305-338).
+    """
+    dtype = w.ln_w.dtype
+    zd = z.to(dtype)
+    h = F.relu(F.linear(F.layer_norm(zd, (zd.shape[-1],), w.ln_w, w.ln_b, eps), w.w1, w.b1))
+    y = F.linear(h, w.w2, w.b2)
+    if mask is not None:
+        m = mask if mask.dim() == y.dim() else mask.unsqueeze(-1)
+        y = y * m.to(dtype)
+    return y + zd if residual else y
+
+
 # ------------------------------------------------------------------------------------------ triangle multiplication
 
 OUTGOING = 0

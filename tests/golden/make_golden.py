@@ -168,8 +168,45 @@ def main() -> None:
     save("transition", x=x, mask=tmask, out_residual_masked=ref_res, out_update=ref_upd, out_module_update_masked=mod_upd,
          out_module_update_masked_bf16=mod_upd16, **{f"w_{k}": v for k, v in tw.items()})
 
+    relu_transition_case()
     trimul_cases()
     single_track_cases()
+
+
+def relu_transition_case() -> None:
+    """ReLU pair transition: the reference's fused-kernel reference function (activation="relu") and the eager body
+    of its PairTransition module (``_forward_impl``), fp32 and bf16.  The module's FusedLayerNorm takes CUDA tensors
+    only, so its ``layer_norm`` attribute is replaced by a plain ``torch.nn.LayerNorm`` with the same parameters."""
+    from bionemo_ir._torch.custom_ops.transition_mlp_w_norm import transition_mlp_w_norm_reference
+    from bionemo_ir._torch.layers.transition import PairTransition
+
+    g = torch.Generator().manual_seed(1005)
+    x = torch.randn(2, 12, 12, 128, generator=g).bfloat16().float()
+    w = {
+        "w1": (torch.randn(512, 128, generator=g) * 0.05).bfloat16().float(),
+        "b1": (0.1 * torch.randn(512, generator=g)).bfloat16().float(),
+        "w2": (torch.randn(128, 512, generator=g) * 0.05).bfloat16().float(),
+        "b2": (0.1 * torch.randn(128, generator=g)).bfloat16().float(),
+        "ln_w": (1 + 0.2 * torch.randn(128, generator=g)).bfloat16().float(),
+        "ln_b": (0.2 * torch.randn(128, generator=g)).bfloat16().float(),
+    }
+    mask = (torch.rand(2, 12, 12, generator=g) > 0.3).float()
+    ref_res = transition_mlp_w_norm_reference(x, mask, w["ln_w"], w["ln_b"], w["w1"], w["b1"], w["w2"], w["b2"], 1e-5,
+                                              activation="relu", residual=True)
+    ref_upd = transition_mlp_w_norm_reference(x, None, w["ln_w"], w["ln_b"], w["w1"], w["b1"], w["w2"], w["b2"], 1e-5,
+                                              activation="relu", residual=False)
+    out = {}
+    for name, dtype in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        layer = PairTransition(128, 4, dtype=dtype, skip_create_weights=True)
+        layer.layer_norm = torch.nn.LayerNorm(128, eps=1e-5)
+        layer.layer_norm.weight.data.copy_(w["ln_w"])
+        layer.layer_norm.bias.data.copy_(w["ln_b"])
+        layer = layer.to(dtype)
+        set_linear(layer.linear_1, w["w1"].to(dtype), w["b1"].to(dtype))
+        set_linear(layer.linear_2, w["w2"].to(dtype), w["b2"].to(dtype))
+        out[f"out_module_residual_masked_{name}"] = layer._forward_impl(x.to(dtype), mask.to(dtype), residual=True)
+    save("pair_transition_relu", x=x, mask=mask, out_residual_masked=ref_res, out_update=ref_upd, **out,
+         **{f"w_{k}": v for k, v in w.items()})
 
 
 def single_track_cases() -> None:

@@ -351,6 +351,43 @@ def test_transition_without_norm():
     assert (t(x).float() - want).abs().max() < 2e-3
 
 
+def build_relu_transition(w: orc.ReluTransitionWeights) -> b200.PairTransition:
+    t = b200.PairTransition(128, 4, dtype=torch.bfloat16)
+    t.load_state_dict({"layer_norm.weight": w.ln_w, "layer_norm.bias": w.ln_b, "linear_1.weight": w.w1,
+                       "linear_1.bias": w.b1, "linear_2.weight": w.w2, "linear_2.bias": w.b2}, strict=True)
+    return t.to(DEV)
+
+
+def test_relu_pair_transition_matches_reference_outputs():
+    g = load_golden("pair_transition_relu")
+    w = orc.ReluTransitionWeights(g["w_ln_w"], g["w_ln_b"], g["w_w1"], g["w_b1"], g["w_w2"], g["w_b2"])
+    t = build_relu_transition(w)
+    x = g["x"].to(DEV).bfloat16()
+    torch.testing.assert_close(t(x, g["mask"].to(DEV), residual=True).float().cpu(), g["out_residual_masked"],
+                               rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(t(x).float().cpu(), g["out_update"], rtol=RTOL, atol=ATOL)
+    assert (t(x).float().cpu() - g["out_update"]).abs().max() < 1e-2  # |update| ~ 1: a bf16 ulp or two
+
+
+@pytest.mark.parametrize("shape", [(1, 128), (3, 5, 7), (2, 130, 130), (1, 1), (1, 300, 300)])
+def test_relu_pair_transition_sweep(shape):
+    torch.manual_seed(sum(shape) + 1)
+    w = bf16_weights(orc.make_relu_transition_weights(25))
+    t = build_relu_transition(w)
+    x = torch.randn(*shape, 128).bfloat16().to(DEV)
+    mask = (torch.rand(*shape, device=DEV) > 0.25).float()
+    wd = orc.ReluTransitionWeights(*[p.to(DEV) for p in w.__dict__.values()])
+    torch.testing.assert_close(t(x, residual=True).float(), orc.relu_transition_forward(x.float(), None, wd, residual=True),
+                               rtol=RTOL, atol=ATOL)
+    upd = t(x, mask)
+    torch.testing.assert_close(upd.float(), orc.relu_transition_forward(x.float(), mask, wd), rtol=RTOL, atol=ATOL)
+    assert (upd.float()[mask == 0] == 0).all()  # masked rows get no update (bias included)
+    assert torch.equal(t(x.transpose(0, 1) if x.dim() > 2 else x, residual=True),
+                       t(x, residual=True).transpose(0, 1) if x.dim() > 2 else t(x, residual=True))
+    with pytest.raises(ValueError):
+        b200.PairTransition(256, 4, dtype=torch.bfloat16)
+
+
 # ------------------------------------------------------------------------------------------ lifecycle
 
 

@@ -343,3 +343,23 @@ def test_numa_binding_is_a_no_op_without_a_readable_topology():
     else:
         assert set(cores) <= set(before) and sorted(__import__("os").sched_getaffinity(0)) == cores
         __import__("os").sched_setaffinity(0, before)
+
+
+def test_weight_packing_refuses_host_tensors():
+    """A host address must never reach a kernel: packing checks the device before anything is launched."""
+    from bionemo_inference_runtime_b200 import ops
+
+    with pytest.raises(ValueError, match="CUDA device"):
+        ops.pack_transition_weights(torch.ones(128), torch.zeros(128), torch.zeros(1024, 128), torch.zeros(128, 512))
+    with pytest.raises(ValueError, match="CUDA device"):
+        ops.pack_relu_transition_weights(torch.ones(128), torch.zeros(128), torch.zeros(512, 128), torch.zeros(512),
+                                         torch.zeros(128, 512), torch.zeros(128))
+
+
+def test_pair_transition_state_dict_contract():
+    t = b200.PairTransition(128, 4, dtype=torch.bfloat16)
+    assert {k: tuple(v.shape) for k, v in t.state_dict().items()} == {
+        "layer_norm.weight": (128,), "layer_norm.bias": (128,), "linear_1.weight": (512, 128), "linear_1.bias": (512,),
+        "linear_2.weight": (128, 512), "linear_2.bias": (128,)}
+    with pytest.raises(ValueError):
+        b200.PairTransition(64, 4, dtype=torch.bfloat16)

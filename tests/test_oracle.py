@@ -124,3 +124,15 @@ def test_single_track_transition_matches_the_reference_module():
     torch.testing.assert_close(orc.transition_forward(g["t_x"], None, w), g["t_update"], rtol=1e-4, atol=1e-5)
     got16 = orc.transition_forward(g["t_x"].bfloat16(), None, w.to(torch.bfloat16))
     torch.testing.assert_close(got16.float(), g["t_update_bf16"], rtol=2e-2, atol=4e-2)
+
+
+def test_relu_transition_matches_reference_outputs():
+    g = load_golden("pair_transition_relu")
+    w = orc.ReluTransitionWeights(g["w_ln_w"], g["w_ln_b"], g["w_w1"], g["w_b1"], g["w_w2"], g["w_b2"])
+    torch.testing.assert_close(orc.relu_transition_forward(g["x"], g["mask"], w, residual=True), g["out_residual_masked"],
+                               rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(orc.relu_transition_forward(g["x"], None, w), g["out_update"], rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(orc.relu_transition_forward(g["x"], g["mask"], w, residual=True),
+                               g["out_module_residual_masked_fp32"], rtol=1e-6, atol=1e-6)
+    got16 = orc.relu_transition_forward(g["x"].bfloat16(), g["mask"].bfloat16(), w.to(torch.bfloat16), residual=True)
+    assert (got16.float() - g["out_module_residual_masked_bf16"]).abs().max() <= 0.03125  # one bf16 ulp at |z| < 8
