@@ -27,7 +27,7 @@ from .buffers import PreallocatedBuffers
 from .transition import Transition
 from .triangle_multiplication import (TriangleMultiplicationMetadata, TriangleMultiplicationNode,
                                       TriangleMultiplicationNodeType, precompute_trimul_metadata)
-from .triangle_nodes import TriangleAttentionEndingNode, TriangleAttentionStartingNode
+from .triangle_nodes import TriangleAttentionEndingNode, TriangleAttentionStartingNode, _weight_state
 
 
 class PairformerLayerV1(nn.Module):
@@ -211,7 +211,9 @@ class PairformerModule(nn.Module):
         if not (self.use_cuda_graph and z.is_cuda) or torch.cuda.is_current_stream_capturing():
             return self._run(s, z, mask, pair_mask, attn_metadatas, buffers, **kwargs)
         inputs = (s, z, mask, pair_mask)
-        key = tuple((tuple(t.shape), t.dtype, t.device) for t in inputs)
+        # the recorded kernels hold the addresses of the layers' packed weights: a reload or an in-place edit of
+        # any parameter must record a new graph
+        key = (*((tuple(t.shape), t.dtype, t.device) for t in inputs), _weight_state(*self.parameters()))
         if self._graph is None or key != self._graph_key:
             static = [t.clone() for t in inputs]
             graph_buffers: dict = {}
@@ -286,7 +288,9 @@ class PairformerNoSeqModule(nn.Module):
             return z
         if not (self.use_cuda_graph and z.is_cuda) or torch.cuda.is_current_stream_capturing():
             return self._run(z, pair_mask, attn_metadatas, buffers, **kwargs)
-        key = (tuple(z.shape), z.dtype, z.device, tuple(pair_mask.shape), pair_mask.dtype)
+        # the recorded kernels hold the addresses of the layers' packed weights: a reload or an in-place edit of
+        # any parameter must record a new graph
+        key = (tuple(z.shape), z.dtype, z.device, tuple(pair_mask.shape), pair_mask.dtype, _weight_state(*self.parameters()))
         if self._graph is None or key != self._graph_key:
             self._graph_in, self._graph_mask = z.clone(), pair_mask.clone()
             graph_buffers: dict = {}

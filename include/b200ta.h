@@ -234,6 +234,8 @@ int b200ta_node_forward(const void* z, int64_t zs_b, int64_t zs_r, int64_t zs_s,
  * larger problems are refused with B200TA_ERR_UNSUPPORTED and a message, and belong to b200ta_node_forward.
  * The call makes no cudaMalloc/cudaFree and calls no allocating routine.  Its first call on a device looks up
  * the array's device address (with that device current); make that first call before starting a stream capture.
+ * The looked-up address is kept per device for the life of the process: it does not survive a cudaDeviceReset
+ * or any other teardown of the device's context, after which this entry point must not be called again.
  * Every call uses the one array and leaves its last intermediates there, so two calls that can overlap on the
  * GPU (different streams, or different host threads without ordering) race on it: order them on one stream
  * or with events.  Nothing in the array needs clearing between calls: each call writes all it later reads.

@@ -139,9 +139,9 @@ def node_stages(z: torch.Tensor, mask: torch.Tensor | None, w: NodeWeights, node
 
     qh, kh, vh = heads_first(q), heads_first(k), heads_first(v)
     a = torch.matmul(qh, kh.transpose(-1, -2))  # [B, R, H, S, S]
-    a = a / math.sqrt(d)
-    a = a + mb
-    a = a + tb.unsqueeze(1)
+    a /= math.sqrt(d)  # in place, as the reference's eager backend does (vanilla.py:61-67)
+    a += mb
+    a += tb.unsqueeze(1)
     p = F.softmax(a, dim=-1)
     o = torch.matmul(p, vh)  # [B, R, H, S, d]
     o = o.transpose(-3, -2).reshape(B, R, S, heads * d)
@@ -211,9 +211,9 @@ def node_forward_rows(z: torch.Tensor, mask: torch.Tensor | None, w: NodeWeights
         return t.reshape(B, r, S, heads, d).permute(0, 1, 3, 2, 4)
 
     a = torch.matmul(heads_first(q), heads_first(k).transpose(-1, -2))
-    a = a / math.sqrt(d)
-    a = a + additive_mask_bias(m_s, inf, dtype)
-    a = a + tb.unsqueeze(1)
+    a /= math.sqrt(d)  # in place, as the reference's eager backend does (vanilla.py:61-67)
+    a += additive_mask_bias(m_s, inf, dtype)
+    a += tb.unsqueeze(1)
     o = torch.matmul(F.softmax(a, dim=-1), heads_first(v)).transpose(-3, -2).reshape(B, r, S, heads * d)
     update = F.linear(o * torch.sigmoid(g), w.w_out, w.b_out)
     return x_s + update if residual else update

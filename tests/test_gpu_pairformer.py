@@ -84,6 +84,13 @@ def test_two_blocks_match_the_oracle_and_the_graph_replay_matches_eager(backend)
     assert torch.equal(first, out) and torch.equal(again, out)
     z2 = torch.randn(1, n, n, 128).bfloat16().to(DEV)
     assert torch.equal(graphed(z2, mask.to(DEV)), stack(z2, mask.to(DEV)))
+    # new weights after the graph was recorded: the next call must not replay kernels that hold the old packs
+    other = _state_dict([_block_weights(300), _block_weights(400)])
+    graphed.load_state_dict(other, strict=True)
+    stack.load_state_dict(other, strict=True)
+    fresh = stack(z2, mask.to(DEV))
+    assert not torch.equal(fresh, out)
+    assert torch.equal(graphed(z2, mask.to(DEV)), fresh)
 
 
 def test_padded_tokens_stay_finite_and_valid_region_matches():
