@@ -512,14 +512,16 @@ NVLINK_GBS = 900.0  # per direction per GPU, the figure the config-5 roofline is
 
 def sharded_check(args, world: int, rank: int, device) -> dict:
     """The sharded block against the same modules on one GPU, on a tensor small enough to hold whole on rank 0:
-    z[1, 512, 512, 128], 475 valid tokens, one block, the exchange form the benchmark uses.  Every rank takes part;
+    z[1, 512, 512, 128] (1024 tokens on 8 ranks), the last 37 tokens padded, one block, the exchange form the
+    benchmark uses.  Every rank takes part;
     rank 0 compares.  The block runs twice when the transposes are fused (the second call reuses the
     symmetric-memory shards, as consecutive blocks of the benchmark do)."""
     import torch.distributed as dist
 
     from bionemo_inference_runtime_b200 import sharded
 
-    N, valid = 512, 475
+    N = max(512, 128 * world)  # at least 128 pair rows per rank
+    valid = N - 37
     n = N // world
     z = torch.randn(1, N, N, 128, generator=torch.Generator().manual_seed(77)).bfloat16().to(device)
     start, end, trans = build_modules(node_weights(7001), node_weights(7002), transition_weights(7003), device)
@@ -714,8 +716,9 @@ def run_sharded(args) -> dict:
         "roofline": {"kernel": "attention_kernel", "bound": "tensor", "achieved": attn_flops / attn_ms / 1e9,
                      "peak": peak_tf, "unit": "TFLOP/s", "frac": attn_flops / attn_ms / 1e9 / peak_tf,
                      "peak_source": f"{peak_kind} bf16 burst", "ms_per_launch": attn_ms,
-                     "traffic": TRAFFIC.get(args.workload),
-                     "note": "rank 0's shard of one starting node; algorithmic flops = 512 x valid keys per valid position"},
+                     "traffic": TRAFFIC[args.workload] / world,
+                     "note": "rank 0's shard of one starting node; algorithmic flops = 512 x valid keys per valid position; "
+                             "traffic scaled by pair positions from the ncu capture of the 512-token launch"},
         "roofline_block": {"definition": "max(flops / bf16 peak, 3 x 512 B per position / HBM) per GPU + bytes of the two "
                                          "transposes / 900 GB/s", "flops_ms": t_flops, "hbm_ms": t_bytes,
                            "links_ms": t_links, "roofline_ms": t_roof, "block_ms": block_ms, "frac": t_roof / block_ms,
@@ -745,8 +748,13 @@ def run_sharded(args) -> dict:
     return result
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per attention launch, from the committed ncu summaries (profiles/)
-TRAFFIC: dict[str, float | None] = {"cfg2": 341.5e6, "cfg3": None, "n768": None}
+# dram__bytes_read.sum + dram__bytes_write.sum per attention launch, from the committed ncu summary of the cfg2
+# capture (profiles/attention_kernel_cfg2.md: 270.6 MB read + 53.4 MB written for 512 x 512 positions).  The traffic is
+# the q / k / v / gate planes read once and the output written once, i.e. proportional to the pair positions of the
+# launch, so the larger workloads scale that capture by their positions (cfg5: one rank's shard of a node).
+TRAFFIC_PER_POSITION = 324.0e6 / (512 * 512)
+TRAFFIC: dict[str, float | None] = {"cfg2": 324.0e6, "cfg3": None, "n768": TRAFFIC_PER_POSITION * 768 * 768,
+                                    "cfg5": TRAFFIC_PER_POSITION * 4096 * 4096}
 
 
 def cpu_sample(cfg: dict, rows: int, threads: int):
