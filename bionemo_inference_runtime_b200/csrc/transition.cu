@@ -14,7 +14,11 @@
 // GEMM2 of chunk j so the tensor core runs while the SwiGLU warps work.
 //
 // Warp roles (384 threads): warps 0-3 / 4-7 SwiGLU + output warpgroups (even / odd chunks),
-// warp 8 TMA producer, warp 9 MMA issuer / TMEM owner, warps 10-11 idle.
+// warp 8 TMA producer of x and W1, warp 11 TMA producer of W2, warp 9 GEMM1 issuer / TMEM owner, warp 10 GEMM2 issuer.  The two GEMMs have
+// an issuing warp each because one thread issues a tcgen05.mma only about every 80-110 clocks: the 12 MMAs of a
+// chunk issued from one thread took 1100 of the 1500 clocks a chunk cost.  A SwiGLU warpgroup computes the next
+// tile's LayerNorm statistics before it waits for the current tile's last GEMM2, so the tile switch costs the
+// tensor core little.
 #include "common.cuh"
 #include "layout.h"
 
@@ -68,6 +72,30 @@ enum Bar {
 
 constexpr uint32_t kTmemAcc1 = 0, kTmemAcc2 = 256, kTmemCols = 512;
 
+// Mean / rstd of row m of an x tile in shared memory ([2 channel halves][128 rows][64 ch], 128-byte swizzle), as
+// rstd and -mean * rstd.
+__device__ __forceinline__ void row_statistics(uint32_t x0, int m, float eps, float& rstd, float& nmr) {
+  uint32_t v[64];
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    uint4 x = lds128(x0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
+    v[c * 4 + 0] = x.x, v[c * 4 + 1] = x.y, v[c * 4 + 2] = x.z, v[c * 4 + 3] = x.w;
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 64; ++j) sum += bf16_lo(v[j]) + bf16_hi(v[j]);
+  const float mu = sum * (1.f / kC);
+  float var = 0.f;
+#pragma unroll
+  for (int j = 0; j < 64; ++j) {
+    const float d0 = bf16_lo(v[j]) - mu, d1 = bf16_hi(v[j]) - mu;
+    var = fmaf(d0, d0, var);
+    var = fmaf(d1, d1, var);
+  }
+  rstd = rsqrtf(var * (1.f / kC) + eps);
+  nmr = -mu * rstd;
+}
+
 template <bool kRelu>
 __global__ void __launch_bounds__(kThreads, 1)
 transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w1,
@@ -119,27 +147,32 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 
   const int my_tiles = (p.num_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1;
 
+  // Register budget: 168 per thread at launch; the helper warpgroup hands registers to the two SwiGLU warpgroups,
+  // which hold a whole accumulator row (128 values) at a time: 128 x 56 + 256 x 224 = 384 x 168.
+  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer of x tiles and W1 chunks
+    // (what GEMM1 needs; W2 has its own producer so that a W2 slot that frees late never holds back a W1 load)
     if (lane == 0) {
       tma_prefetch_desc(&tm_x);
       tma_prefetch_desc(&tm_w1);
-      tma_prefetch_desc(&tm_w2);
       tma_prefetch_desc(&tm_outs.m[0]);
       bool ok = true;
       int c = 0;  // chunk counter
-      for (int i = 0; ok && i < my_tiles; ++i) {
-        const int tile = blockIdx.x + i * gridDim.x;
+      auto load_x = [&](int i) -> bool {
         const int xs = i & 1;
-        ok = mbar_wait(bars + (X_EMPTY + xs) * 8, ((i >> 1) & 1) ^ 1, abort_flag);
-        if (!ok) break;
+        if (!mbar_wait(bars + (X_EMPTY + xs) * 8, ((i >> 1) & 1) ^ 1, abort_flag)) return false;
         mbar_expect_tx(bars + (X_FULL + xs) * 8, 32768);
+        const int tile = blockIdx.x + i * gridDim.x;
         tma_load_2d(base + kSmX + xs * 32768, &tm_x, bars + (X_FULL + xs) * 8, 0, tile * kTileM);
         tma_load_2d(base + kSmX + xs * 32768 + 16384, &tm_x, bars + (X_FULL + xs) * 8, 64, tile * kTileM);
+        return true;
+      };
+      ok = load_x(0);
+      for (int i = 0; ok && i < my_tiles; ++i) {
         for (int j = 0; j < kChunks; ++j, ++c) {
           const int st = c & 1;
-          const uint32_t par = ((c >> 1) & 1) ^ 1;
-          ok = mbar_wait(bars + (W1_EMPTY + st) * 8, par, abort_flag);
+          ok = mbar_wait(bars + (W1_EMPTY + st) * 8, ((c >> 1) & 1) ^ 1, abort_flag);
           if (!ok) break;
           const uint32_t f1 = bars + (W1_FULL + st) * 8;
           mbar_expect_tx(f1, 32768);
@@ -148,7 +181,28 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             tma_load_2d(dst, &tm_w1, f1, kh * 64, j * kChunk);                  // value rows
             tma_load_2d(dst + 8192, &tm_w1, f1, kh * 64, kHidden + j * kChunk);  // gate rows
           }
-          ok = mbar_wait(bars + (W2_EMPTY + st) * 8, par, abort_flag);
+          // the next tile's rows, early enough for its statistics to be taken before this tile ends
+          if (j == 3 && i + 1 < my_tiles) {
+            ok = load_x(i + 1);
+            if (!ok) break;
+          }
+        }
+      }
+      if (*abort_flag && c > 0) {
+        const int last = c - 1;
+        mbar_wait(bars + (W1_FULL + (last & 1)) * 8, (last >> 1) & 1, abort_flag + 1);
+      }
+    }
+  } else if (warp == 11) {
+    // ------------------------------------------------------------------ TMA producer of W2 chunks
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_w2);
+      bool ok = true;
+      int c = 0;
+      for (int i = 0; ok && i < my_tiles; ++i) {
+        for (int j = 0; j < kChunks; ++j, ++c) {
+          const int st = c & 1;
+          ok = mbar_wait(bars + (W2_EMPTY + st) * 8, ((c >> 1) & 1) ^ 1, abort_flag);
           if (!ok) break;
           const uint32_t f2 = bars + (W2_FULL + st) * 8;
           mbar_expect_tx(f2, 16384);
@@ -161,156 +215,149 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       }
     }
   } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ GEMM1 issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(kTileM, 128);
       bool ok = true;
-      int c1 = 0, c2 = 0;  // GEMM1 / GEMM2 chunk counters
+      int c1 = 0;  // chunk counter
       for (int i = 0; ok && i < my_tiles; ++i) {
         const int xs = i & 1;
         ok = mbar_wait(bars + (X_FULL + xs) * 8, (i >> 1) & 1, abort_flag);
         if (!ok) break;
-        for (int j = 0; ok && j <= kChunks; ++j) {
-          if (j < kChunks) {
-            const int e = c1 & 1;
-            const uint32_t par = (c1 >> 1) & 1;
-            ok = mbar_wait(bars + (W1_FULL + e) * 8, par, abort_flag) &&
-                 mbar_wait(bars + (ACC1_FREE + e) * 8, par ^ 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            // one descriptor per operand; each K step adds a constant to the address field (16-byte units)
-            const uint64_t da = make_smem_desc(base + kSmX + xs * 32768, 16, 1024, kLayoutSw128);
-            const uint64_t db = make_smem_desc(base + kSmW1 + e * 32768, 16, 1024, kLayoutSw128);
-            const uint32_t d1 = tmem_base + kTmemAcc1 + e * 128;
+        for (int j = 0; ok && j < kChunks; ++j, ++c1) {
+          const int e = c1 & 1;
+          const uint32_t par = (c1 >> 1) & 1;
+          ok = mbar_wait(bars + (W1_FULL + e) * 8, par, abort_flag) &&
+               mbar_wait(bars + (ACC1_FREE + e) * 8, par ^ 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          // one descriptor per operand; each K step adds a constant to the address field (16-byte units)
+          const uint64_t da = make_smem_desc(base + kSmX + xs * 32768, 16, 1024, kLayoutSw128);
+          const uint64_t db = make_smem_desc(base + kSmW1 + e * 32768, 16, 1024, kLayoutSw128);
+          const uint32_t d1 = tmem_base + kTmemAcc1 + e * 128;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const uint32_t off = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-              umma_ss(d1, da + off, db + off, idesc, k > 0 ? 1u : 0u);
-            }
-            umma_commit(bars + (ACC1_FULL + e) * 8);
-            umma_commit(bars + (W1_EMPTY + e) * 8);
-            if (j == kChunks - 1) umma_commit(bars + (X_EMPTY + xs) * 8);
-            ++c1;
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
+            umma_ss(d1, da + off, db + off, idesc, k > 0 ? 1u : 0u);
           }
-          if (j > 0) {
-            const int jj = j - 1;
-            const int e = c2 & 1;
-            const uint32_t par = (c2 >> 1) & 1;
-            ok = mbar_wait(bars + (W2_FULL + e) * 8, par, abort_flag) &&
-                 mbar_wait(bars + (H_FULL + e) * 8, par, abort_flag);
-            if (ok && jj == 0) ok = mbar_wait(bars + (ACC2_FREE + (i & 1)) * 8, ((i >> 1) & 1) ^ 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            const uint64_t dh = make_smem_desc(base + kSmH + e * 16384, 16, 1024, kLayoutSw128);
-            const uint64_t dw = make_smem_desc(base + kSmW2 + e * 16384, 16, 1024, kLayoutSw128);
-            const uint32_t d2 = tmem_base + kTmemAcc2 + (i & 1) * 128;
-            umma_ss(d2, dh, dw, idesc, jj > 0 ? 1u : 0u);
+          umma_commit(bars + (ACC1_FULL + e) * 8);
+          umma_commit(bars + (W1_EMPTY + e) * 8);
+          if (j == kChunks - 1) umma_commit(bars + (X_EMPTY + xs) * 8);
+        }
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ GEMM2 issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(kTileM, 128);
+      bool ok = true;
+      int c2 = 0;  // chunk counter
+      for (int i = 0; ok && i < my_tiles; ++i) {
+        for (int jj = 0; ok && jj < kChunks; ++jj, ++c2) {
+          const int e = c2 & 1;
+          const uint32_t par = (c2 >> 1) & 1;
+          ok = mbar_wait(bars + (W2_FULL + e) * 8, par, abort_flag) &&
+               mbar_wait(bars + (H_FULL + e) * 8, par, abort_flag);
+          if (ok && jj == 0) ok = mbar_wait(bars + (ACC2_FREE + (i & 1)) * 8, ((i >> 1) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t dh = make_smem_desc(base + kSmH + e * 16384, 16, 1024, kLayoutSw128);
+          const uint64_t dw = make_smem_desc(base + kSmW2 + e * 16384, 16, 1024, kLayoutSw128);
+          const uint32_t d2 = tmem_base + kTmemAcc2 + (i & 1) * 128;
+          umma_ss(d2, dh, dw, idesc, jj > 0 ? 1u : 0u);
 #pragma unroll
-            for (int k = 1; k < 4; ++k) umma_ss(d2, dh + k * 2, dw + k * 2, idesc, 1u);
-            umma_commit(bars + (W2_EMPTY + e) * 8);
-            umma_commit(bars + (H_FREE + e) * 8);
-            if (jj == kChunks - 1) umma_commit(bars + (ACC2_FULL + (i & 1)) * 8);
-            ++c2;
-          }
+          for (int k = 1; k < 4; ++k) umma_ss(d2, dh + k * 2, dw + k * 2, idesc, 1u);
+          umma_commit(bars + (W2_EMPTY + e) * 8);
+          umma_commit(bars + (H_FREE + e) * 8);
+          if (jj == kChunks - 1) umma_commit(bars + (ACC2_FULL + (i & 1)) * 8);
         }
       }
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ SwiGLU / output warpgroups
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int e = warp >> 2;               // chunk parity and output column half this warpgroup owns
     const int m = (warp & 3) * 32 + lane;  // row inside the tile == TMEM lane
     const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     const uint32_t slab = base + kSmOut + warp * 2048;
     bool ok = true;
     int n = 0;  // uses of this warpgroup's acc1 / H buffers
+    const bool normalize = __ldg(p.flags) != 0;
+    float rstd = 1.f, nmr = 0.f;  // LayerNorm statistics of row m of the current tile
     for (int i = 0; ok && i < my_tiles; ++i) {
       const int tile = blockIdx.x + i * gridDim.x;
       const int xs = i & 1;
       const long long row = (long long)tile * kTileM + m;
-      ok = mbar_wait(bars + (X_FULL + xs) * 8, (i >> 1) & 1, abort_flag);
-      if (!ok) break;
-      // LayerNorm statistics of row m
       const uint32_t x0 = base + kSmX + xs * 32768;
-      float rstd = 1.f, nmr = 0.f;
-      if (__ldg(p.flags) != 0) {
-        uint32_t v[64];
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          uint4 x = lds128(x0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
-          v[c * 4 + 0] = x.x, v[c * 4 + 1] = x.y, v[c * 4 + 2] = x.z, v[c * 4 + 3] = x.w;
-        }
-        float sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < 64; ++j) sum += bf16_lo(v[j]) + bf16_hi(v[j]);
-        const float mu = sum * (1.f / kC);
-        float var = 0.f;
-#pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const float d0 = bf16_lo(v[j]) - mu, d1 = bf16_hi(v[j]) - mu;
-          var = fmaf(d0, d0, var);
-          var = fmaf(d1, d1, var);
-        }
-        rstd = rsqrtf(var * (1.f / kC) + p.eps);
-        nmr = -mu * rstd;
+      if (i == 0) {
+        ok = mbar_wait(bars + (X_FULL + xs) * 8, 0, abort_flag);
+        if (!ok) break;
+        if (normalize) row_statistics(x0, m, p.eps, rstd, nmr);
       }
       for (int j = e; ok && j < kChunks; j += 2, ++n) {
-        ok = mbar_wait(bars + (ACC1_FULL + e) * 8, n & 1, abort_flag) &&
-             mbar_wait(bars + (H_FREE + e) * 8, (n & 1) ^ 1, abort_flag);
+        ok = mbar_wait(bars + (ACC1_FULL + e) * 8, n & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
+        // The whole accumulator (64 value and 64 gate columns of this row) goes to registers first, so that it is
+        // free for the chunk after next while this one is still being computed.
+        uint32_t xv[64], xg[64];
+        const uint32_t acc1 = lane_taddr + kTmemAcc1 + e * 128;
+        tmem_ld32(acc1, reinterpret_cast<uint32_t(&)[32]>(xv[0]));
+        tmem_ld32(acc1 + 32, reinterpret_cast<uint32_t(&)[32]>(xv[32]));
+        if (!kRelu) {
+          tmem_ld32(acc1 + 64, reinterpret_cast<uint32_t(&)[32]>(xg[0]));
+          tmem_ld32(acc1 + 96, reinterpret_cast<uint32_t(&)[32]>(xg[32]));
+        }
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + (ACC1_FREE + e) * 8);
         const float4* scv = reinterpret_cast<const float4*>(gen + kSmSc) + j * (kChunk / 2);               // value pairs
         const float4* scg = reinterpret_cast<const float4*>(gen + kSmSc) + kHidden / 2 + j * (kChunk / 2);  // gate pairs
         const uint64_t rstd2 = pack_f32x2(rstd, rstd), nmr2 = pack_f32x2(nmr, nmr);
-        // 16 hidden units at a time; the TMEM loads of the next step are in flight while this one is computed
-        uint32_t av[2][16], ag[2][16];
-        const uint32_t acc1 = lane_taddr + kTmemAcc1 + e * 128;
-        tmem_ld16(acc1, av[0]);
-        tmem_ld16(acc1 + 64, ag[0]);
+        uint32_t pk[32];
 #pragma unroll
-        for (int qt = 0; qt < 4; ++qt) {
-          tmem_ld_wait();
-          if (qt + 1 < 4) {
-            tmem_ld16(acc1 + (qt + 1) * 16, av[(qt + 1) & 1]);
-            tmem_ld16(acc1 + 64 + (qt + 1) * 16, ag[(qt + 1) & 1]);
+        for (int t = 0; t < 32; ++t) {
+          // two hidden units at a time, packed fp32x2 math
+          const float4 cv = scv[t];
+          const uint64_t val2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xv[2 * t]), __uint_as_float(xv[2 * t + 1])),
+                                          fma_f32x2(nmr2, pack_f32x2(cv.x, cv.y), pack_f32x2(cv.z, cv.w)));
+          float o0, o1;
+          if (kRelu) {
+            unpack_f32x2(val2, o0, o1);
+            o0 = fmaxf(o0, 0.f), o1 = fmaxf(o1, 0.f);
+          } else {
+            const float4 cg = scg[t];
+            const uint64_t h2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xg[2 * t]), __uint_as_float(xg[2 * t + 1])),
+                                          fma_f32x2(nmr2, pack_f32x2(cg.x, cg.y), pack_f32x2(cg.z, cg.w)));  // gate / 2
+            float h0, h1;
+            unpack_f32x2(h2, h0, h1);
+            // silu(gate) * value = (h * tanh(h) + h) * value
+            const uint64_t hid2 = mul_f32x2(fma_f32x2(h2, pack_f32x2(tanh_approx(h0), tanh_approx(h1)), h2), val2);
+            unpack_f32x2(hid2, o0, o1);
           }
-          const uint32_t (&xv)[16] = av[qt & 1];
-          const uint32_t (&xg)[16] = ag[qt & 1];
-          uint32_t pk[8];
-#pragma unroll
-          for (int t = 0; t < 8; ++t) {
-            // two hidden units at a time, packed fp32x2 math
-            const float4 cv = scv[qt * 8 + t], cg = scg[qt * 8 + t];
-            const uint64_t val2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xv[2 * t]), __uint_as_float(xv[2 * t + 1])),
-                                            fma_f32x2(nmr2, pack_f32x2(cv.x, cv.y), pack_f32x2(cv.z, cv.w)));
-            float o0, o1;
-            if (kRelu) {
-              unpack_f32x2(val2, o0, o1);
-              o0 = fmaxf(o0, 0.f), o1 = fmaxf(o1, 0.f);
-            } else {
-              const uint64_t h2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xg[2 * t]), __uint_as_float(xg[2 * t + 1])),
-                                            fma_f32x2(nmr2, pack_f32x2(cg.x, cg.y), pack_f32x2(cg.z, cg.w)));  // gate / 2
-              float h0, h1;
-              unpack_f32x2(h2, h0, h1);
-              // silu(gate) * value = (h * tanh(h) + h) * value
-              const uint64_t hid2 = mul_f32x2(fma_f32x2(h2, pack_f32x2(tanh_approx(h0), tanh_approx(h1)), h2), val2);
-              unpack_f32x2(hid2, o0, o1);
-            }
-            pk[t] = pack_bf16x2(o0, o1);
-          }
-#pragma unroll
-          for (int c = 0; c < 2; ++c)
-            sts128(base + kSmH + e * 16384 + sw128_offset(m, qt * 2 + c),
-                   make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]));
+          pk[t] = pack_bf16x2(o0, o1);
         }
-        tc_fence_before();
+        // the H buffer's previous use (two chunks back) must have been consumed by its GEMM2
+        ok = mbar_wait(bars + (H_FREE + e) * 8, (n & 1) ^ 1, abort_flag);
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          sts128(base + kSmH + e * 16384 + sw128_offset(m, c),
+                 make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]));
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bars + (ACC1_FREE + e) * 8);
-          mbar_arrive(bars + (H_FULL + e) * 8);
-        }
+        if (lane == 0) mbar_arrive(bars + (H_FULL + e) * 8);
       }
       if (!ok) break;
+      // The next tile's statistics now, while the tensor core finishes this tile's last GEMM2 (its rows are in the
+      // other X buffer already): the tile switch then only costs the output below.
+      float next_rstd = 1.f, next_nmr = 0.f;
+      if (i + 1 < my_tiles) {
+        ok = mbar_wait(bars + (X_FULL + (xs ^ 1)) * 8, ((i + 1) >> 1) & 1, abort_flag);
+        if (!ok) break;
+        if (normalize) row_statistics(base + kSmX + (xs ^ 1) * 32768, m, p.eps, next_rstd, next_nmr);
+      }
       // ---- output: columns [64e, 64e+64) of acc2 (+ residual) (* mask)
       const int ab = i & 1;
       ok = mbar_wait(bars + (ACC2_FULL + ab) * 8, (i >> 1) & 1, abort_flag);
@@ -375,6 +422,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         mbar_arrive(bars + (ACC2_FREE + ab) * 8);
         mbar_arrive(bars + (X_EMPTY + xs) * 8);
       }
+      rstd = next_rstd, nmr = next_nmr;
     }
     if (lane == 0) tma_store_wait_all();
   }
