@@ -48,6 +48,12 @@ SIGNATURES: dict[str, tuple] = {
          c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_float, c_int, c_int, c_int,
          c_int, c_int, c_void_p],
     ),
+    "b200ta_attention_masked": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+         c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p,
+         c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ),
     "b200ta_epilogue": (
         c_int,
         [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,

@@ -46,6 +46,8 @@ struct AttnParams {
   int num_items;  // B * 4 * q_pairs * R
   const int32_t* lengths;
   long long ls_b, ls_r;
+  const uint32_t* key_mask;  // masked form: bit k of word [b][r][k / 32] = key k takes part (0 at and past the length)
+  long long km_b, km_r;      // strides of key_mask in words
   const __nv_bfloat16* gate;
   long long g_br, g_h, g_s;
   __nv_bfloat16* out;
@@ -177,6 +179,7 @@ __device__ __forceinline__ void cursor_next(const AttnParams& p, TileCursor& c, 
   cursor_seek(p, c, my_items);
 }
 
+template <bool kMasked>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_bias,
@@ -414,6 +417,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       if (w >= it.nvalid) continue;  // this half holds no query of the item
       float row_max = 0.f, row_sum = 0.f;  // row_max: reference point of the exponentials, in raw score units
+      bool have_anchor = false;            // masked form: a key tile with a valid key has been seen
       uint4 gv[4];                               // gate row, fetched during the last key tile
 #pragma unroll
       for (int j = 0; j < 4; ++j) gv[j] = make_uint4(0, 0, 0, 0);
@@ -474,16 +478,32 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // The reference point of the exponentials is the maximum of the item's first key tile.  Later tiles
         // skip the search for a maximum: fp32 sums, fp32 O and bf16 P share the fp32 exponent range, so
         // probabilities far above 1 lose nothing, and a tile whose sum leaves the safe range is redone below.
-        if (kt == 0) {
-          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
+        bool find_anchor = kt == 0;
+        if (kMasked) {
+          // Keys may be switched off anywhere in the row (the same bits for every query of this item).  A tile
+          // without any valid key yields zeros (the reference point stays 0 until a tile with a valid key comes).
+          const uint32_t* mrow = p.key_mask + it.b * p.km_b + it.r * p.km_r + kt * 4;
+          const int words = (p.S + 31) >> 5;
+          uint32_t mw[4];
 #pragma unroll
-          for (int j = 0; j < 64; ++j) mx[j & 3] = max3_f32(mx[j & 3], s2[2 * j], s2[2 * j + 1]);
-          row_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));  // finite: key 0 of the first tile is valid
-        } else {
+          for (int j = 0; j < 4; ++j) mw[j] = kt * 4 + j < words ? __ldg(mrow + j) : 0u;
+#pragma unroll
+          for (int j = 0; j < 128; ++j)
+            if (!((mw[j >> 5] >> (j & 31)) & 1u)) s2[j] = -INFINITY;
+          find_anchor = !have_anchor && (mw[0] | mw[1] | mw[2] | mw[3]) != 0u;
+          have_anchor = have_anchor || find_anchor;
+        }
+        if (kt > 0) {
           // the previous tile's P·V must be complete before P is overwritten
           ok = mbar_wait(bars + (O_FULL + w) * 8, (ct - 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
+        }
+        if (find_anchor) {
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
+#pragma unroll
+          for (int j = 0; j < 64; ++j) mx[j & 3] = max3_f32(mx[j & 3], s2[2 * j], s2[2 * j + 1]);
+          row_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));  // finite: the tile holds a valid key
         }
         // p = 2^(c * (s - row_max)); bf16 pairs go back to TMEM as the A operand of P·V
         float tile_sum;
@@ -632,13 +652,14 @@ void fast_div_constants(uint32_t d, uint32_t* mul, uint32_t* shr) {
 }  // namespace
 }  // namespace b200ta
 
-extern "C" {
+namespace b200ta {
+namespace {
 
-int b200ta_attention(const void* q, const void* k, const void* v, const void* gate, int64_t s_br, int64_t s_h,
+int launch_attention(const void* q, const void* k, const void* v, const void* gate, int64_t s_br, int64_t s_h,
                      int64_t s_s, const void* bias, int64_t bs_b, int64_t bs_h, int64_t bs_q,
-                     const int32_t* lengths, int64_t ls_b, int64_t ls_r, void* out, int64_t os_br, int64_t os_s,
-                     int64_t os_h, float* lse, float softmax_scale, int empty_row_mode, int B, int R, int S,
-                     int S_pad, void* stream) {
+                     const int32_t* lengths, int64_t ls_b, int64_t ls_r, const uint32_t* key_mask, int64_t km_b,
+                     int64_t km_r, void* out, int64_t os_br, int64_t os_s, int64_t os_h, float* lse,
+                     float softmax_scale, int empty_row_mode, int B, int R, int S, int S_pad, void* stream) {
   using namespace b200ta;
   B200TA_REQUIRE(q && k && v && bias && out, "attention: NULL pointer");
   B200TA_REQUIRE(B > 0 && R > 0 && S > 0, "attention: bad sizes B=%d R=%d S=%d", B, R, S);
@@ -684,6 +705,8 @@ int b200ta_attention(const void* q, const void* k, const void* v, const void* ga
   fast_div_constants(uint32_t(q_pairs), &p.qp_mul, &p.qp_shr);
   p.lengths = lengths;
   p.ls_b = ls_b, p.ls_r = ls_r;
+  p.key_mask = key_mask;
+  p.km_b = km_b, p.km_r = km_r;
   p.gate = static_cast<const __nv_bfloat16*>(gate);
   p.g_br = s_br, p.g_h = s_h, p.g_s = s_s;
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -694,11 +717,43 @@ int b200ta_attention(const void* q, const void* k, const void* v, const void* ga
   p.wide_store = (reinterpret_cast<uintptr_t>(out) & 31u) == 0 && os_br % 16 == 0 && os_s % 16 == 0 && os_h % 16 == 0;
   p.status = st->status_dev;
 
-  B200TA_CHECK_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmDynamic));
   const int grid = p.num_items < st->num_sms ? p.num_items : st->num_sms;
-  attention_kernel<<<grid, kThreads, kSmDynamic, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, tm_bias, p);
+  if (key_mask != nullptr) {
+    B200TA_REQUIRE(lengths != nullptr, "attention: the masked form needs the row lengths (last valid key + 1) as well");
+    B200TA_CHECK_CUDA(cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmDynamic));
+    attention_kernel<true><<<grid, kThreads, kSmDynamic, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, tm_bias, p);
+  } else {
+    B200TA_CHECK_CUDA(cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmDynamic));
+    attention_kernel<false><<<grid, kThreads, kSmDynamic, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, tm_bias, p);
+  }
   B200TA_CHECK_CUDA(cudaGetLastError());
   return B200TA_OK;
+}
+
+}  // namespace
+}  // namespace b200ta
+
+extern "C" {
+
+int b200ta_attention(const void* q, const void* k, const void* v, const void* gate, int64_t s_br, int64_t s_h,
+                     int64_t s_s, const void* bias, int64_t bs_b, int64_t bs_h, int64_t bs_q,
+                     const int32_t* lengths, int64_t ls_b, int64_t ls_r, void* out, int64_t os_br, int64_t os_s,
+                     int64_t os_h, float* lse, float softmax_scale, int empty_row_mode, int B, int R, int S,
+                     int S_pad, void* stream) {
+  return b200ta::launch_attention(q, k, v, gate, s_br, s_h, s_s, bias, bs_b, bs_h, bs_q, lengths, ls_b, ls_r, nullptr, 0,
+                                  0, out, os_br, os_s, os_h, lse, softmax_scale, empty_row_mode, B, R, S, S_pad, stream);
+}
+
+int b200ta_attention_masked(const void* q, const void* k, const void* v, const void* gate, int64_t s_br, int64_t s_h,
+                            int64_t s_s, const void* bias, int64_t bs_b, int64_t bs_h, int64_t bs_q,
+                            const int32_t* lengths, int64_t ls_b, int64_t ls_r, const uint32_t* key_mask,
+                            int64_t km_b, int64_t km_r, void* out, int64_t os_br, int64_t os_s, int64_t os_h,
+                            float* lse, float softmax_scale, int empty_row_mode, int B, int R, int S, int S_pad,
+                            void* stream) {
+  if (key_mask == nullptr) return b200ta::fail(B200TA_ERR_INVALID, "attention_masked: key_mask must not be NULL");
+  return b200ta::launch_attention(q, k, v, gate, s_br, s_h, s_s, bias, bs_b, bs_h, bs_q, lengths, ls_b, ls_r, key_mask,
+                                  km_b, km_r, out, os_br, os_s, os_h, lse, softmax_scale, empty_row_mode, B, R, S, S_pad,
+                                  stream);
 }
 
 }  // extern "C"

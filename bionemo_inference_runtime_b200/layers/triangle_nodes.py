@@ -153,9 +153,6 @@ class TriangleAttentionNode(nn.Module):
             mha_bias_flags = {"q": False, "k": False, "v": False, "g": False, "o": False}
         if empty_row_mode not in _EMPTY_ROW_MODES:
             raise ValueError(f"empty_row_mode must be one of {sorted(_EMPTY_ROW_MODES)}")
-        if not pair_mask_left_aligned:
-            raise ValueError("the sm_100a triangle-attention kernel masks keys by row length and therefore needs "
-                             "left-aligned (1…1 0…0) pair masks (pair_mask_left_aligned=True)")
         self.c_in = c_in
         self.c_hidden = c_hidden
         self.num_heads = num_heads
@@ -226,7 +223,20 @@ class TriangleAttentionNode(nn.Module):
         ending = self.node_type == TriangleAttentionNodeType.ENDING
         B, N = x.shape[0], x.shape[1]
         R = S = N
-        if mask_bias is None:
+        key_mask = None
+        if not self.pair_mask_left_aligned and (mask is not None or mask_bias is not None):
+            # keys may be switched off anywhere in a row: the kernel takes one bit per key beside the row lengths
+            if mask_bias is None:
+                valid = (mask.transpose(1, 2) if ending else mask) > 0.5
+            elif mask_bias.dtype == torch.int32:
+                raise ValueError("a node built with pair_mask_left_aligned=False takes the pair mask or its additive "
+                                 "form ([B, R, 1, 1, S]); int32 row lengths describe left-aligned masks only")
+            else:
+                valid = (mask_bias[:, :, 0, 0, :] if mask_bias.dim() == 5 else mask_bias) >= 0
+            if tuple(valid.shape) != (B, R, S):
+                raise ValueError(f"mask of shape {tuple(valid.shape)} does not match the pair tensor [B={B}, {R}, {S}]")
+            lengths, key_mask = ops.key_mask_bits(valid)
+        elif mask_bias is None:
             if mask is None:
                 lengths = None
             else:
@@ -243,7 +253,7 @@ class TriangleAttentionNode(nn.Module):
 
         policy = self.mha.chunk_policy
         chunked = policy is not None and policy.should_chunk(xk) and policy.chunk_size < R
-        if not chunked and not self.transposed_bias:
+        if not chunked and not self.transposed_bias and key_mask is None:
             # common case: one library call for the whole node, intermediates in one workspace
             ws = ensure_buffer(buffers, "tri_attn_workspace", (ops.node_workspace_bytes(B, N),), torch.uint8, x.device)
             return ops.node_forward(x, packed, lengths, eps, ending=ending, residual=residual, out=out, workspace=ws,
@@ -269,7 +279,8 @@ class TriangleAttentionNode(nn.Module):
             og = ensure_buffer(buffers, "tri_attn_output", (B * length, S, ops.HEADS, ops.HEAD_DIM), torch.bfloat16,
                                x.device)
             og = ops.attention(qkvg, bias, None if lengths is None else lengths.narrow(1, start, length), B, length, S,
-                               out=None if og is None else og.view(B, length, S, ops.C), empty_row_mode=mode)
+                               out=None if og is None else og.view(B, length, S, ops.C), empty_row_mode=mode,
+                               key_mask=None if key_mask is None else key_mask.narrow(1, start, length))
             ops.epilogue(og, packed, xs if residual else None, outk.narrow(1, start, length))
         return out
 

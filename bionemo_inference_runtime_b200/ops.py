@@ -140,11 +140,13 @@ def prologue(z, packed, eps: float = 1e-5, *, ending: bool = False, want_qkvg: b
 
 def attention(qkvg: torch.Tensor, bias: torch.Tensor, lengths: torch.Tensor | None, B: int, R: int, S: int, *,
               gate: bool = True, out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
-              empty_row_mode: int = _lib.EMPTY_ROW_UNIFORM, scale: float | None = None) -> torch.Tensor:
+              empty_row_mode: int = _lib.EMPTY_ROW_UNIFORM, scale: float | None = None,
+              key_mask: torch.Tensor | None = None) -> torch.Tensor:
     """Biased, length-masked attention over the head-major ``qkvg`` planes; returns ``[B, R, S, 128]``.
 
     ``bias`` is the triangle bias times ``BIAS_SCALE`` and, with ``gate``, the g plane holds gate factors in
-    [0, 1] (sigmoid already applied) - the forms ``prologue`` writes.
+    [0, 1] (sigmoid already applied) - the forms ``prologue`` writes.  ``key_mask`` (int32 ``[B, R, ceil(S/32)]``,
+    from :func:`key_mask_bits`) switches single keys of a row off; ``lengths`` must then be the bits' row lengths.
     """
     _require_cuda_bf16("qkvg", qkvg)
     _require_cuda_bf16("bias", bias)
@@ -170,11 +172,35 @@ def attention(qkvg: torch.Tensor, bias: torch.Tensor, lengths: torch.Tensor | No
         if t.stride() != q.stride():
             raise ValueError("q, k, v, g planes must share strides")
     o4 = out.view(B * R, S, HEADS, HEAD_DIM)
-    _lib.call("b200ta_attention", q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr() if gate else None,
-              q.stride(0), q.stride(1), q.stride(2), bias.data_ptr(), bias.stride(0), bias.stride(1), bias.stride(2),
-              _ptr(lengths), *ls, o4.data_ptr(), o4.stride(0), o4.stride(1), o4.stride(2), _ptr(lse), float(scale),
-              int(empty_row_mode), B, R, S, bias.shape[-1], _stream())
+    head = (q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr() if gate else None, q.stride(0), q.stride(1), q.stride(2),
+            bias.data_ptr(), bias.stride(0), bias.stride(1), bias.stride(2), _ptr(lengths), *ls)
+    tail = (o4.data_ptr(), o4.stride(0), o4.stride(1), o4.stride(2), _ptr(lse), float(scale), int(empty_row_mode), B, R, S,
+            bias.shape[-1], _stream())
+    if key_mask is None:
+        _lib.call("b200ta_attention", *head, *tail)
+    else:
+        words = (S + 31) // 32
+        if (key_mask.dtype != torch.int32 or not key_mask.is_cuda or tuple(key_mask.shape) != (B, R, words)
+                or key_mask.stride(2) != 1 or lengths is None or lengths.numel() != B * R):
+            raise ValueError(f"key_mask must be a CUDA int32 tensor [B={B}, R={R}, {words}] with unit word stride, "
+                             "passed together with its [B, R] row lengths")
+        _lib.call("b200ta_attention_masked", *head, key_mask.data_ptr(), key_mask.stride(0), key_mask.stride(1), *tail)
     return out
+
+
+def key_mask_bits(valid: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``valid`` ``[B, R, S]`` (bool: key t of pair row (b, r) takes part) -> (row lengths ``[B, R]`` int32 = last
+    valid key + 1, bit words ``[B, R, ceil(S/32)]`` int32 with bit ``t % 32`` of word ``t // 32`` set for valid keys):
+    the payload of ``attention(..., key_mask=...)`` for masks that are not left-aligned."""
+    B, R, S = valid.shape
+    words = (S + 31) // 32
+    position = torch.arange(1, S + 1, device=valid.device, dtype=torch.int32)
+    lengths = (valid.to(torch.int32) * position).amax(dim=-1).contiguous()
+    padded = torch.zeros((B, R, words * 32), dtype=torch.int64, device=valid.device)
+    padded[..., :S] = valid
+    weights = torch.ones(32, dtype=torch.int64, device=valid.device) << torch.arange(32, device=valid.device)
+    bits = (padded.view(B, R, words, 32) * weights).sum(dim=-1)
+    return lengths, bits.to(torch.int32).contiguous()  # the conversion wraps: bit 31 becomes the sign bit
 
 
 def node_workspace_bytes(B: int, N: int) -> int:

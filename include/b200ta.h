@@ -177,6 +177,23 @@ int b200ta_attention(const void* q, const void* k, const void* v, const void* ga
                      int empty_row_mode, int B, int R, int S, int S_pad, void* stream);
 
 /*
+ * The same attention core with keys that may be switched off anywhere in a row (pair masks that are not
+ * 1…1 0…0).  key_mask holds one bit per key: bit (t % 32) of the 32-bit word at b*km_b + r*km_r + t/32 is 1 when
+ * key t of pair row (b, r) takes part; ceil(S / 32) words per row, bits at and past the row's length 0.
+ * lengths (required here) is the position of the row's last valid key + 1 (0 = no valid key: empty_row_mode
+ * applies).  All queries of a pair row share its bits.  Otherwise as b200ta_attention.
+ * Replaces: the additive-mask backends the reference uses when a node is built with
+ * pair_mask_left_aligned=False (bionemo_ir/_torch/layers/triangle_nodes.py:230-246,
+ * bionemo_ir/_torch/attention_backend/utils.py:305-317).
+ */
+int b200ta_attention_masked(const void* q, const void* k, const void* v, const void* gate, int64_t s_br,
+                            int64_t s_h, int64_t s_s, const void* bias, int64_t bs_b, int64_t bs_h,
+                            int64_t bs_q, const int32_t* lengths, int64_t ls_b, int64_t ls_r,
+                            const uint32_t* key_mask, int64_t km_b, int64_t km_r, void* out, int64_t os_br,
+                            int64_t os_s, int64_t os_h, float* lse, float softmax_scale, int empty_row_mode,
+                            int B, int R, int S, int S_pad, void* stream);
+
+/*
  * Epilogue: out = residual + og · W_oᵀ + b_o, with og = o ⊙ sigmoid(g) as written by
  * b200ta_attention.
  *

@@ -146,6 +146,37 @@ def test_config2_shape_with_padding():
     torch.testing.assert_close(z2.float(), want2, rtol=RTOL, atol=ATOL)
 
 
+@pytest.mark.parametrize("node_type", [orc.STARTING, orc.ENDING])
+def test_masks_that_are_not_left_aligned(node_type):
+    """``pair_mask_left_aligned=False``: keys switched off anywhere in a row (holes, a first key tile without any
+    valid key, a single valid key at the end, rows without a valid key), as the 0/1 mask and in its additive form."""
+    torch.manual_seed(15 + node_type)
+    n = 200
+    w = bf16_weights(orc.make_node_weights(37, identity_ln=False, gate_bias=1.0))
+    z = torch.randn(2, n, n, 128).bfloat16()
+    mask = (torch.rand(2, n, n) > 0.4).float()
+    rows = mask if node_type == orc.STARTING else mask.transpose(1, 2)  # [b, pair row of the node, key]
+    rows[0, 3, :130] = 0      # no valid key in the first key tile
+    rows[0, 4] = 0
+    rows[0, 4, n - 1] = 1     # a single valid key, the last one
+    rows[0, 5] = 0            # no valid key at all
+    rows[1, 7, :] = 1
+    rows[1, 8, 64:128] = 0
+    dev_w = orc.NodeWeights(*[None if t is None else t.to(DEV) for t in
+                              (w.ln_w, w.ln_b, w.w_bias, w.w_in, w.b_in, w.w_out, w.b_out)])
+    want = orc.node_forward(z.float().to(DEV), mask.to(DEV), dev_w, node_type, residual=True)
+    node = build_node(w, node_type, pair_mask_left_aligned=False)
+    out = node(z.to(DEV), mask=mask.to(DEV), residual=True)
+    torch.testing.assert_close(out.float(), want, rtol=RTOL, atol=ATOL)
+    pre = b200.precompute_pair_masks("VANILLA", mask.to(DEV), dtype=torch.bfloat16)
+    bias = pre.mask_bias if node_type == orc.STARTING else pre.mask_bias_transposed
+    assert torch.equal(node(z.to(DEV), mask_bias=bias, residual=True), out)
+    chunky = build_node(w, node_type, pair_mask_left_aligned=False, chunk_policy=b200.ChunkPolicy(chunk_size=64, min_size=1))
+    assert torch.equal(chunky(z.to(DEV), mask=mask.to(DEV), residual=True), out)
+    with pytest.raises(ValueError, match="left-aligned"):
+        node(z.to(DEV), mask_bias=torch.full((2, n), n, dtype=torch.int32, device=DEV))
+
+
 def test_ending_equals_transposed_starting_bit_for_bit():
     torch.manual_seed(3)
     w = bf16_weights(orc.make_node_weights(3, identity_ln=False))

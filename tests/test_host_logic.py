@@ -110,8 +110,8 @@ def test_layers_refuse_cpu_tensors_and_other_dtypes():
         node(torch.zeros(1, 8, 8, 128, dtype=torch.bfloat16))
     with pytest.raises(ValueError, match="bfloat16"):
         b200.TriangleAttentionStartingNode(128, 32, 4, dtype=torch.float32)(torch.zeros(1, 8, 8, 128))
-    with pytest.raises(ValueError):
-        b200.TriangleAttentionStartingNode(128, 32, 4, dtype=torch.bfloat16, pair_mask_left_aligned=False)
+    general = b200.TriangleAttentionStartingNode(128, 32, 4, dtype=torch.bfloat16, pair_mask_left_aligned=False)
+    assert general.pair_mask_left_aligned is False  # keys masked by bits instead of row lengths
     with pytest.raises(ValueError, match="CUDA"):
         b200.Transition(128, 512, dtype=torch.bfloat16)(torch.zeros(4, 128, dtype=torch.bfloat16))
 
