@@ -154,10 +154,15 @@ struct TileCursor {
   bool valid;
 };
 
+// kWarp: called by all lanes of a converged warp; the row length read from memory is broadcast from lane 0 so
+// that everything derived from it is the same in every lane by construction (warp-uniform code).
+template <bool kWarp = false>
 __device__ __forceinline__ void cursor_seek(const AttnParams& p, TileCursor& c, int my_items) {
   // positions the cursor on the first item with work at or after c.i
   while (c.i < my_items) {
-    c.it = decode_item(p, blockIdx.x + c.i * gridDim.x);
+    int len = item_raw_length(p, blockIdx.x + c.i * gridDim.x);
+    if (kWarp) len = __shfl_sync(0xffffffffu, len, 0);
+    c.it = decode_item(p, blockIdx.x + c.i * gridDim.x, len);
     if (!c.it.skip) {
       c.valid = true;
       return;
@@ -166,17 +171,19 @@ __device__ __forceinline__ void cursor_seek(const AttnParams& p, TileCursor& c, 
   }
   c.valid = false;
 }
+template <bool kWarp = false>
 __device__ __forceinline__ void cursor_init(const AttnParams& p, TileCursor& c, int my_items) {
   c.i = 0, c.kt = 0, c.g = 0, c.qi = 0;
-  cursor_seek(p, c, my_items);
+  cursor_seek<kWarp>(p, c, my_items);
 }
+template <bool kWarp = false>
 __device__ __forceinline__ void cursor_next(const AttnParams& p, TileCursor& c, int my_items) {
   ++c.g;
   if (++c.kt < c.it.nkt) return;
   c.kt = 0;
   ++c.qi;
   ++c.i;
-  cursor_seek(p, c, my_items);
+  cursor_seek<kWarp>(p, c, my_items);
 }
 
 template <bool kMasked>
@@ -297,28 +304,30 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
   } else if (warp == 9 || warp == 11) {
     // ------------------------------------------------------------------ score MMA issuers (S = Q·Kᵀ + I·Bias)
-    // One warp per 128-query half (a single thread issues a tcgen05.mma about every 80 clocks, so the ten MMAs
-    // of a half per key tile are issued side by side).  Each runs one key tile ahead of the softmax (also across
+    // One warp per 128-query half.  All 32 lanes run the loop with the same values and one elected lane issues
+    // (umma_*_warp): a converged warp issues its MMAs at the rate the tensor pipe retires them, a single thread
+    // inside a branch needs 45-80 clocks per MMA.  Each warp runs one key tile ahead of the softmax (also across
     // work items): the only thing it waits for besides the loads is that its half's S buffer has been read out.
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc_s = make_idesc_bf16(kQTile, kKTile);                // Q·Kᵀ: both operands K-major
       constexpr uint32_t idesc_b1 = make_idesc_bf16(kQTile, 128, false, true);     // I·Bias: B MN-major
-      const int w = warp == 9 ? 0 : 1;
-      const uint32_t ti = tmem_base + kTmemI;
-      const uint32_t d = tmem_base + kTmemS + w * 128;  // S of this half
-      int n = 0;                                        // S tiles issued (phase of S_FREE)
+      const int w = __shfl_sync(0xffffffffu, warp == 9 ? 0 : 1, 0);
+      const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
+      const uint32_t ti = tb + kTmemI;
+      const uint32_t d = tb + kTmemS + w * 128;  // S of this half
+      int n = 0;                                 // S tiles issued (phase of S_FREE)
       bool ok = true;
       TileCursor c;
-      cursor_init(p, c, my_items);
+      cursor_init<true>(p, c, my_items);
       while (ok && c.valid) {
         const Item& it = c.it;
         const int ib = c.qi & 1, stage = c.g % kStages;
-        if (c.kt == 0) ok = mbar_wait(bars + (Q_FULL + ib) * 8, (c.qi >> 1) & 1, abort_flag);
-        ok = ok && mbar_wait(bars + (KB_FULL + stage) * 8, (c.g / kStages) & 1, abort_flag);
+        if (c.kt == 0) ok = mbar_wait_warp(bars + (Q_FULL + ib) * 8, (c.qi >> 1) & 1, abort_flag);
+        ok = ok && mbar_wait_warp(bars + (KB_FULL + stage) * 8, (c.g / kStages) & 1, abort_flag);
         if (!ok) break;
         if (w < it.nvalid) {
           // One descriptor per operand tile; the K steps only add a constant to its address field (in 16-byte
-          // units), which keeps this single-thread issue path down to a few instructions per MMA.
+          // units).
           const uint32_t sbase = base + kSmStage + stage * kStageBytes;
           const uint64_t dk = make_smem_desc(sbase, 16, 512, kLayoutSw64);
           const uint64_t dq = make_smem_desc(base + kSmQ + ib * 16384 + w * 8192, 16, 512, kLayoutSw64);
@@ -326,65 +335,66 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           // 64-127 of half 0, then of half 1.  As B[key][query] this is MN-major with 16 query rows (2 KiB)
           // per K step.
           const uint64_t db = make_smem_desc(sbase + 8192 + w * 32768, 16384, 1024, kLayoutSw128);
-          ok = mbar_wait(bars + (S_FREE + w) * 8, (n & 1) ^ 1, abort_flag);
+          ok = mbar_wait_warp(bars + (S_FREE + w) * 8, (n & 1) ^ 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
           if (!it.uniform) {  // a row without a valid key has equal logits: the softmax warps need no scores
-            umma_ss(d, dq, dk, idesc_s, 0u);
-            umma_ss(d, dq + 2, dk + 2, idesc_s, 1u);  // second 16 channels: +32 bytes
+            umma_ss_warp(d, dq, dk, idesc_s, 0u);
+            umma_ss_warp(d, dq + 2, dk + 2, idesc_s, 1u);  // second 16 channels: +32 bytes
 #pragma unroll
-            for (int j = 0; j < 8; ++j) umma_ts(d, ti + j * 8, db + j * 128, idesc_b1, 1u);
+            for (int j = 0; j < 8; ++j) umma_ts_warp(d, ti + j * 8, db + j * 128, idesc_b1, 1u);
           }
-          umma_commit(bars + (S_FULL + w) * 8);
+          umma_commit_warp(bars + (S_FULL + w) * 8);
           ++n;
-          umma_commit(bars + (KB_EMPTY + stage) * 8);                      // K and bias are free once both halves' MMAs ran
-          if (c.kt == it.nkt - 1) umma_commit(bars + (Q_EMPTY + ib) * 8);  // last use of this item's Q
+          umma_commit_warp(bars + (KB_EMPTY + stage) * 8);  // K and bias are free once both halves' MMAs ran
+          if (c.kt == it.nkt - 1) umma_commit_warp(bars + (Q_EMPTY + ib) * 8);  // last use of this item's Q
         } else {
           // this half holds no query of the item: only keep the shared barriers' counts complete
-          mbar_arrive(bars + (KB_EMPTY + stage) * 8);
-          if (c.kt == it.nkt - 1) mbar_arrive(bars + (Q_EMPTY + ib) * 8);
+          mbar_arrive_warp(bars + (KB_EMPTY + stage) * 8);
+          if (c.kt == it.nkt - 1) mbar_arrive_warp(bars + (Q_EMPTY + ib) * 8);
         }
-        cursor_next(p, c, my_items);
+        cursor_next<true>(p, c, my_items);
       }
     }
   } else if (warp == 10) {
-    // ------------------------------------------------------------------ P·V MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ P·V MMA issuer (warp-collective as well)
+    {
       constexpr uint32_t idesc_o = make_idesc_bf16(kQTile, kHeadDim, false, true);  // P·V: B is MN-major
+      const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
       int n0 = 0, n1 = 0;  // P tiles consumed per half
       bool ok = true;
       TileCursor c;
-      cursor_init(p, c, my_items);
+      cursor_init<true>(p, c, my_items);
       while (ok && c.valid) {
         const Item& it = c.it;
         const int vs = c.g % kVStages;
-        ok = mbar_wait(bars + (V_FULL + vs) * 8, (c.g / kVStages) & 1, abort_flag);
+        ok = mbar_wait_warp(bars + (V_FULL + vs) * 8, (c.g / kVStages) & 1, abort_flag);
         const uint64_t dv = make_smem_desc(base + kSmV + vs * 8192, 16, 512, kLayoutSw64);
         const uint32_t acc0 = c.kt > 0 ? 1u : 0u;
-        ok = ok && mbar_wait(bars + (P_FULL + 0) * 8, n0 & 1, abort_flag);
+        ok = ok && mbar_wait_warp(bars + (P_FULL + 0) * 8, n0 & 1, abort_flag);
         if (!ok) break;
         ++n0;
         tc_fence_after();
         {
-          const uint32_t d = tmem_base + kTmemO, tp = tmem_base + kTmemP;
-          umma_ts(d, tp, dv, idesc_o, acc0);
+          const uint32_t d = tb + kTmemO, tp = tb + kTmemP;
+          umma_ts_warp(d, tp, dv, idesc_o, acc0);
 #pragma unroll
-          for (int j = 1; j < 8; ++j) umma_ts(d, tp + j * 8, dv + j * 64, idesc_o, 1u);  // 16 keys = 1 KiB per step
-          umma_commit(bars + (O_FULL + 0) * 8);
+          for (int j = 1; j < 8; ++j) umma_ts_warp(d, tp + j * 8, dv + j * 64, idesc_o, 1u);  // 16 keys = 1 KiB per step
+          umma_commit_warp(bars + (O_FULL + 0) * 8);
         }
         if (it.nvalid == 2) {
-          ok = mbar_wait(bars + (P_FULL + 1) * 8, n1 & 1, abort_flag);
+          ok = mbar_wait_warp(bars + (P_FULL + 1) * 8, n1 & 1, abort_flag);
           if (!ok) break;
           ++n1;
           tc_fence_after();
-          const uint32_t d = tmem_base + kTmemO + 32, tp = tmem_base + kTmemP + 64;
-          umma_ts(d, tp, dv, idesc_o, acc0);
+          const uint32_t d = tb + kTmemO + 32, tp = tb + kTmemP + 64;
+          umma_ts_warp(d, tp, dv, idesc_o, acc0);
 #pragma unroll
-          for (int j = 1; j < 8; ++j) umma_ts(d, tp + j * 8, dv + j * 64, idesc_o, 1u);
-          umma_commit(bars + (O_FULL + 1) * 8);
+          for (int j = 1; j < 8; ++j) umma_ts_warp(d, tp + j * 8, dv + j * 64, idesc_o, 1u);
+          umma_commit_warp(bars + (O_FULL + 1) * 8);
         }
-        umma_commit(bars + (V_EMPTY + vs) * 8);
-        cursor_next(p, c, my_items);
+        umma_commit_warp(bars + (V_EMPTY + vs) * 8);
+        cursor_next<true>(p, c, my_items);
       }
     }
   } else if (warp < 8) {

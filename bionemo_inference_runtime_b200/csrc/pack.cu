@@ -70,6 +70,16 @@ __global__ void convert_kernel(const void* src, int dtype, size_t n, __nv_bfloat
   if (dst_f32 != nullptr) dst_f32[i] = v;
 }
 
+__global__ void set_flag_kernel(int* flags, int value) { flags[0] = value; }
+
+// The transition's LayerNorm vectors as floats (gamma | beta) and its "apply the LayerNorm" flag.
+void pack_transition_layernorm(const void* ln_w, const void* ln_b, int dtype, char* base, cudaStream_t s) {
+  float* ln = reinterpret_cast<float*>(base + kTransLnOff);
+  convert_kernel<<<1, kC, 0, s>>>(ln_w, dtype, kC, nullptr, ln);
+  convert_kernel<<<1, kC, 0, s>>>(ln_b, dtype, kC, nullptr, ln + kC);
+  set_flag_kernel<<<1, 1, 0, s>>>(reinterpret_cast<int*>(base + kTransFlagsOff), ln_w != nullptr ? 1 : 0);
+}
+
 int check_dtype(int dtype) {
   if (dtype != B200TA_DTYPE_BF16 && dtype != B200TA_DTYPE_F32)
     return fail(B200TA_ERR_INVALID, "weight_dtype must be B200TA_DTYPE_BF16 or B200TA_DTYPE_F32");
@@ -182,10 +192,13 @@ int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const voi
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   char* base = static_cast<char*>(packed);
   // gate rows are halved: silu(g) = h + h * tanh(h) with h = g / 2
-  fold_rows_kernel<<<kTransRows, kC, 0, s>>>(w1, kTransRows, nullptr, 0, nullptr, ln_w, ln_b, weight_dtype, kHidden,
-                                             kTransRows, 0.5f, reinterpret_cast<__nv_bfloat16*>(base + kTransW1Off),
+  // (the LayerNorm is not folded into these rows: the kernel normalises the rows of x as the eager module does)
+  fold_rows_kernel<<<kTransRows, kC, 0, s>>>(w1, kTransRows, nullptr, 0, nullptr, nullptr, nullptr, weight_dtype,
+                                             kHidden, kTransRows, 0.5f,
+                                             reinterpret_cast<__nv_bfloat16*>(base + kTransW1Off),
                                              reinterpret_cast<float2*>(base + kTransScOff),
                                              reinterpret_cast<int*>(base + kTransFlagsOff));
+  pack_transition_layernorm(ln_w, ln_b, weight_dtype, base, s);
   convert_kernel<<<(kC * kHidden + 255) / 256, 256, 0, s>>>(w2, weight_dtype, size_t(kC) * kHidden,
                                                             reinterpret_cast<__nv_bfloat16*>(base + kTransW2Off), nullptr);
   convert_kernel<<<1, kC, 0, s>>>(nullptr, weight_dtype, kC, nullptr, reinterpret_cast<float*>(base + kTransB2Off));
@@ -206,10 +219,11 @@ int b200ta_pack_relu_transition_weights(const void* ln_w, const void* ln_b, cons
   char* base = static_cast<char*>(packed);
   // the 512 hidden rows (with the first linear's bias in their constant term) take the value half; the gate half
   // is zero and unused by the ReLU form of the kernel
-  fold_rows_kernel<<<kTransRows, kC, 0, s>>>(w1, kHidden, nullptr, 0, b1, ln_w, ln_b, weight_dtype, 0, 0, 1.f,
+  fold_rows_kernel<<<kTransRows, kC, 0, s>>>(w1, kHidden, nullptr, 0, b1, nullptr, nullptr, weight_dtype, 0, 0, 1.f,
                                              reinterpret_cast<__nv_bfloat16*>(base + kTransW1Off),
                                              reinterpret_cast<float2*>(base + kTransScOff),
                                              reinterpret_cast<int*>(base + kTransFlagsOff));
+  pack_transition_layernorm(ln_w, ln_b, weight_dtype, base, s);
   convert_kernel<<<(kC * kHidden + 255) / 256, 256, 0, s>>>(w2, weight_dtype, size_t(kC) * kHidden,
                                                             reinterpret_cast<__nv_bfloat16*>(base + kTransW2Off), nullptr);
   convert_kernel<<<1, kC, 0, s>>>(b2, weight_dtype, kC, nullptr, reinterpret_cast<float*>(base + kTransB2Off));

@@ -33,7 +33,8 @@ constexpr int kChunks = kHidden / kChunk;  // 8
 struct TransParams {
   long long rows;
   int num_tiles;
-  const float2* sc;  // [1024] {rowsum, const} of the folded W1 rows
+  const float2* sc;  // [1024] {unused, bias} of the W1 rows (ReLU form)
+  const float* ln;   // gamma[128] | beta[128]
   const int* flags;  // flags[0] != 0 -> apply LayerNorm statistics
   const float* b2;   // [128] bias of the second linear (ReLU form)
   const __nv_bfloat16* mask;
@@ -61,39 +62,71 @@ constexpr int kSmW2 = kSmW1 + 2 * 32768;       // 2 x 16 KiB: [128 out rows][64 
 constexpr int kSmH = kSmW2 + 2 * 16384;        // 2 x 16 KiB: [128 rows][64 hidden]
 constexpr int kSmOut = kSmH + 2 * 16384;       // 8 warps x 2 KiB staging slabs
 constexpr int kSmSc = kSmOut + 8 * 2048;       // per pair of hidden units {rowsum0, rowsum1, const0, const1}: 256 value pairs, 256 gate pairs
-constexpr int kSmBars = kSmSc + 2 * 4096;
+constexpr int kSmLn = kSmSc + 2 * 4096;        // gamma[128] | beta[128] as floats
+constexpr int kSmBars = kSmLn + 1024;
 constexpr int kSmTotal = kSmBars + 256;
 constexpr int kSmDynamic = kSmTotal + 1024;
 
 enum Bar {
   X_FULL = 0, X_EMPTY = 2, W1_FULL = 4, W1_EMPTY = 6, W2_FULL = 8, W2_EMPTY = 10,
-  ACC1_FULL = 12, ACC1_FREE = 14, H_FULL = 16, H_FREE = 18, ACC2_FULL = 20, ACC2_FREE = 22, NUM_BARS = 24
+  ACC1_FULL = 12, ACC1_FREE = 14, H_FULL = 16, H_FREE = 18, ACC2_FULL = 20, ACC2_FREE = 21, XH_FULL = 22, XH_FREE = 23,
+  NUM_BARS = 24
 };
 
-constexpr uint32_t kTmemAcc1 = 0, kTmemAcc2 = 256, kTmemCols = 512;
+// Tensor memory: two GEMM1 accumulators (64 value + 64 gate columns each), the tile's output accumulator, the
+// tile's rows as the A operand of GEMM1 (128 bf16 channels = 64 columns) and two H buffers (64 bf16 hidden units
+// = 32 columns each) as the A operand of GEMM2.  Both A operands live here and not in shared memory because a
+// tcgen05.mma reads its shared-memory operands again for every instruction: with x and H in shared memory the
+// kernel moved ~216 KB through shared memory per chunk (1700 clocks at 128 B/clk) against 768 clocks of tensor
+// work.
+constexpr uint32_t kTmemAcc1 = 0, kTmemAcc2 = 256, kTmemX = 384, kTmemH = 448, kTmemCols = 512;
 
-// Mean / rstd of row m of an x tile in shared memory ([2 channel halves][128 rows][64 ch], 128-byte swizzle), as
-// rstd and -mean * rstd.
-__device__ __forceinline__ void row_statistics(uint32_t x0, int m, float eps, float& rstd, float& nmr) {
+// Reads row m of an x tile in shared memory ([2 channel halves][128 rows][64 ch], 128-byte swizzle), takes its
+// LayerNorm statistics and stores channel half `e` of the normalised row, rounded to bf16 as the eager module's
+// LayerNorm output is, to tensor memory as the A operand of GEMM1.  `ln` holds {gamma[128], beta[128]} as floats;
+// normalize == false stores the raw row.
+__device__ __forceinline__ void normalise_row_to_tmem(uint32_t x0, int m, int e, bool normalize, float eps,
+                                                      const float* ln, uint32_t taddr) {
   uint32_t v[64];
 #pragma unroll
   for (int c = 0; c < 16; ++c) {
     uint4 x = lds128(x0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
     v[c * 4 + 0] = x.x, v[c * 4 + 1] = x.y, v[c * 4 + 2] = x.z, v[c * 4 + 3] = x.w;
   }
-  float sum = 0.f;
+  uint32_t h[32];  // this warpgroup's 64 channels
 #pragma unroll
-  for (int j = 0; j < 64; ++j) sum += bf16_lo(v[j]) + bf16_hi(v[j]);
-  const float mu = sum * (1.f / kC);
-  float var = 0.f;
+  for (int j = 0; j < 32; ++j) h[j] = e ? v[32 + j] : v[j];
+  if (normalize) {
+    float sum = 0.f;
 #pragma unroll
-  for (int j = 0; j < 64; ++j) {
-    const float d0 = bf16_lo(v[j]) - mu, d1 = bf16_hi(v[j]) - mu;
-    var = fmaf(d0, d0, var);
-    var = fmaf(d1, d1, var);
+    for (int j = 0; j < 64; ++j) sum += bf16_lo(v[j]) + bf16_hi(v[j]);
+    const float mu = sum * (1.f / kC);
+    float var = 0.f;
+#pragma unroll
+    for (int j = 0; j < 64; ++j) {
+      const float d0 = bf16_lo(v[j]) - mu, d1 = bf16_hi(v[j]) - mu;
+      var = fmaf(d0, d0, var);
+      var = fmaf(d1, d1, var);
+    }
+    const float rstd = rsqrtf(var * (1.f / kC) + eps);
+    const float nmr = -mu * rstd;
+    const uint64_t rstd2 = pack_f32x2(rstd, rstd), nmr2 = pack_f32x2(nmr, nmr);
+    const float2* gamma = reinterpret_cast<const float2*>(ln) + e * 32;
+    const float2* beta = reinterpret_cast<const float2*>(ln + kC) + e * 32;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      // gamma * (x - mu) * rstd + beta = x * (rstd * gamma) + (beta - mu * rstd * gamma)
+      const float2 g = gamma[j], bt = beta[j];
+      const uint64_t g2 = pack_f32x2(g.x, g.y);
+      const uint64_t y2 = fma_f32x2(pack_f32x2(bf16_lo(h[j]), bf16_hi(h[j])), mul_f32x2(rstd2, g2),
+                                    fma_f32x2(nmr2, g2, pack_f32x2(bt.x, bt.y)));
+      float y0, y1;
+      unpack_f32x2(y2, y0, y1);
+      h[j] = pack_bf16x2(y0, y1);
+    }
   }
-  rstd = rsqrtf(var * (1.f / kC) + eps);
-  nmr = -mu * rstd;
+  tmem_st32(taddr, h);
+  tmem_st_wait();
 }
 
 template <bool kRelu>
@@ -116,7 +149,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     abort_flag[1] = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + (X_FULL + i) * 8, 1);
-      mbar_init(bars + (X_EMPTY + i) * 8, 9);  // GEMM1 commit + 8 epilogue warps
+      mbar_init(bars + (X_EMPTY + i) * 8, 8);  // the 8 epilogue warps (residual)
       mbar_init(bars + (W1_FULL + i) * 8, 1);
       mbar_init(bars + (W1_EMPTY + i) * 8, 1);
       mbar_init(bars + (W2_FULL + i) * 8, 1);
@@ -125,18 +158,17 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       mbar_init(bars + (ACC1_FREE + i) * 8, 4);
       mbar_init(bars + (H_FULL + i) * 8, 4);
       mbar_init(bars + (H_FREE + i) * 8, 1);
-      mbar_init(bars + (ACC2_FULL + i) * 8, 1);
-      mbar_init(bars + (ACC2_FREE + i) * 8, 8);
     }
+    mbar_init(bars + ACC2_FULL * 8, 1);
+    mbar_init(bars + ACC2_FREE * 8, 8);
+    mbar_init(bars + XH_FULL * 8, 8);
+    mbar_init(bars + XH_FREE * 8, 1);
     fence_mbar_init();
   }
-  // stage the per-unit constants of the folded W1 rows, two units per float4
-  for (int q = threadIdx.x; q < kHidden; q += kThreads) {  // 256 value pairs, then 256 gate pairs
-    const float2 a = p.sc[2 * q], b = p.sc[2 * q + 1];
-    reinterpret_cast<float4*>(gen + kSmSc)[q] = make_float4(a.x, b.x, a.y, b.y);
-  }
-  if (kRelu) {  // the gate half of the constants is unused by the ReLU form: the output bias takes its place
-    __syncthreads();
+  // stage the constants: LayerNorm gamma | beta, and for the ReLU form the two linears' biases
+  if (threadIdx.x < 2 * kC) reinterpret_cast<float*>(gen + kSmLn)[threadIdx.x] = p.ln[threadIdx.x];
+  if (kRelu) {
+    for (int q = threadIdx.x; q < kHidden; q += kThreads) reinterpret_cast<float*>(gen + kSmSc)[q] = p.sc[q].y;
     if (threadIdx.x < kC) reinterpret_cast<float*>(gen + kSmSc + 4096)[threadIdx.x] = p.b2[threadIdx.x];
   }
   if (warp == 9) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
@@ -216,60 +248,61 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ GEMM1 issuer
-    if (lane == 0) {
+    // The whole warp runs the loop with the same values and one elected lane issues (umma_*_warp): a converged
+    // warp issues an MMA at the rate the tensor pipe retires it, a single thread in a branch about half as fast.
+    {
       const uint32_t idesc = make_idesc_bf16(kTileM, 128);
+      const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
       bool ok = true;
       int c1 = 0;  // chunk counter
       for (int i = 0; ok && i < my_tiles; ++i) {
-        const int xs = i & 1;
-        ok = mbar_wait(bars + (X_FULL + xs) * 8, (i >> 1) & 1, abort_flag);
+        ok = mbar_wait_warp(bars + XH_FULL * 8, i & 1, abort_flag);  // the tile's rows are in tensor memory
         if (!ok) break;
         for (int j = 0; ok && j < kChunks; ++j, ++c1) {
           const int e = c1 & 1;
           const uint32_t par = (c1 >> 1) & 1;
-          ok = mbar_wait(bars + (W1_FULL + e) * 8, par, abort_flag) &&
-               mbar_wait(bars + (ACC1_FREE + e) * 8, par ^ 1, abort_flag);
+          ok = mbar_wait_warp(bars + (W1_FULL + e) * 8, par, abort_flag) &&
+               mbar_wait_warp(bars + (ACC1_FREE + e) * 8, par ^ 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
           // one descriptor per operand; each K step adds a constant to the address field (16-byte units)
-          const uint64_t da = make_smem_desc(base + kSmX + xs * 32768, 16, 1024, kLayoutSw128);
           const uint64_t db = make_smem_desc(base + kSmW1 + e * 32768, 16, 1024, kLayoutSw128);
-          const uint32_t d1 = tmem_base + kTmemAcc1 + e * 128;
+          const uint32_t d1 = tb + kTmemAcc1 + e * 128;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
+          for (int k = 0; k < 8; ++k) {  // 16 channels per step: 8 columns of the A operand
             const uint32_t off = (k >> 2) * (16384 >> 4) + (k & 3) * 2;
-            umma_ss(d1, da + off, db + off, idesc, k > 0 ? 1u : 0u);
+            umma_ts_warp(d1, tb + kTmemX + k * 8, db + off, idesc, k > 0 ? 1u : 0u);
           }
-          umma_commit(bars + (ACC1_FULL + e) * 8);
-          umma_commit(bars + (W1_EMPTY + e) * 8);
-          if (j == kChunks - 1) umma_commit(bars + (X_EMPTY + xs) * 8);
+          umma_commit_warp(bars + (ACC1_FULL + e) * 8);
+          umma_commit_warp(bars + (W1_EMPTY + e) * 8);
+          if (j == kChunks - 1) umma_commit_warp(bars + XH_FREE * 8);  // the next tile's rows may replace this tile's
         }
       }
     }
   } else if (warp == 10) {
-    // ------------------------------------------------------------------ GEMM2 issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ GEMM2 issuer (warp-collective as well)
+    {
       const uint32_t idesc = make_idesc_bf16(kTileM, 128);
+      const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
       bool ok = true;
       int c2 = 0;  // chunk counter
       for (int i = 0; ok && i < my_tiles; ++i) {
         for (int jj = 0; ok && jj < kChunks; ++jj, ++c2) {
           const int e = c2 & 1;
           const uint32_t par = (c2 >> 1) & 1;
-          ok = mbar_wait(bars + (W2_FULL + e) * 8, par, abort_flag) &&
-               mbar_wait(bars + (H_FULL + e) * 8, par, abort_flag);
-          if (ok && jj == 0) ok = mbar_wait(bars + (ACC2_FREE + (i & 1)) * 8, ((i >> 1) & 1) ^ 1, abort_flag);
+          ok = mbar_wait_warp(bars + (W2_FULL + e) * 8, par, abort_flag) &&
+               mbar_wait_warp(bars + (H_FULL + e) * 8, par, abort_flag);
+          if (ok && jj == 0) ok = mbar_wait_warp(bars + ACC2_FREE * 8, (i & 1) ^ 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t dh = make_smem_desc(base + kSmH + e * 16384, 16, 1024, kLayoutSw128);
           const uint64_t dw = make_smem_desc(base + kSmW2 + e * 16384, 16, 1024, kLayoutSw128);
-          const uint32_t d2 = tmem_base + kTmemAcc2 + (i & 1) * 128;
-          umma_ss(d2, dh, dw, idesc, jj > 0 ? 1u : 0u);
+          const uint32_t d2 = tb + kTmemAcc2, th = tb + kTmemH + e * 32;
+          umma_ts_warp(d2, th, dw, idesc, jj > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 1; k < 4; ++k) umma_ss(d2, dh + k * 2, dw + k * 2, idesc, 1u);
-          umma_commit(bars + (W2_EMPTY + e) * 8);
-          umma_commit(bars + (H_FREE + e) * 8);
-          if (jj == kChunks - 1) umma_commit(bars + (ACC2_FULL + (i & 1)) * 8);
+          for (int k = 1; k < 4; ++k) umma_ts_warp(d2, th + k * 8, dw + k * 2, idesc, 1u);
+          umma_commit_warp(bars + (W2_EMPTY + e) * 8);
+          umma_commit_warp(bars + (H_FREE + e) * 8);
+          if (jj == kChunks - 1) umma_commit_warp(bars + ACC2_FULL * 8);
         }
       }
     }
@@ -283,7 +316,6 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     bool ok = true;
     int n = 0;  // uses of this warpgroup's acc1 / H buffers
     const bool normalize = __ldg(p.flags) != 0;
-    float rstd = 1.f, nmr = 0.f;  // LayerNorm statistics of row m of the current tile
     for (int i = 0; ok && i < my_tiles; ++i) {
       const int tile = blockIdx.x + i * gridDim.x;
       const int xs = i & 1;
@@ -292,7 +324,12 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       if (i == 0) {
         ok = mbar_wait(bars + (X_FULL + xs) * 8, 0, abort_flag);
         if (!ok) break;
-        if (normalize) row_statistics(x0, m, p.eps, rstd, nmr);
+        // this warpgroup's channel half of the normalised row -> A operand of GEMM1
+        normalise_row_to_tmem(x0, m, e, normalize, p.eps, reinterpret_cast<const float*>(gen + kSmLn),
+                              lane_taddr + kTmemX + e * 32);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + XH_FULL * 8);
       }
       for (int j = e; ok && j < kChunks; j += 2, ++n) {
         ok = mbar_wait(bars + (ACC1_FULL + e) * 8, n & 1, abort_flag);
@@ -312,64 +349,70 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + (ACC1_FREE + e) * 8);
-        const float4* scv = reinterpret_cast<const float4*>(gen + kSmSc) + j * (kChunk / 2);               // value pairs
-        const float4* scg = reinterpret_cast<const float4*>(gen + kSmSc) + kHidden / 2 + j * (kChunk / 2);  // gate pairs
-        const uint64_t rstd2 = pack_f32x2(rstd, rstd), nmr2 = pack_f32x2(nmr, nmr);
         uint32_t pk[32];
+        if (kRelu) {
+          const float2* b1s = reinterpret_cast<const float2*>(gen + kSmSc) + j * (kChunk / 2);
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          // two hidden units at a time, packed fp32x2 math
-          const float4 cv = scv[t];
-          const uint64_t val2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xv[2 * t]), __uint_as_float(xv[2 * t + 1])),
-                                          fma_f32x2(nmr2, pack_f32x2(cv.x, cv.y), pack_f32x2(cv.z, cv.w)));
-          float o0, o1;
-          if (kRelu) {
-            unpack_f32x2(val2, o0, o1);
-            o0 = fmaxf(o0, 0.f), o1 = fmaxf(o1, 0.f);
-          } else {
-            const float4 cg = scg[t];
-            const uint64_t h2 = fma_f32x2(rstd2, pack_f32x2(__uint_as_float(xg[2 * t]), __uint_as_float(xg[2 * t + 1])),
-                                          fma_f32x2(nmr2, pack_f32x2(cg.x, cg.y), pack_f32x2(cg.z, cg.w)));  // gate / 2
-            float h0, h1;
-            unpack_f32x2(h2, h0, h1);
-            // silu(gate) * value = (h * tanh(h) + h) * value
-            const uint64_t hid2 = mul_f32x2(fma_f32x2(h2, pack_f32x2(tanh_approx(h0), tanh_approx(h1)), h2), val2);
-            unpack_f32x2(hid2, o0, o1);
+          for (int t = 0; t < 32; ++t) {
+            const float2 b = b1s[t];
+            pk[t] = pack_bf16x2(fmaxf(__uint_as_float(xv[2 * t]) + b.x, 0.f), fmaxf(__uint_as_float(xv[2 * t + 1]) + b.y, 0.f));
           }
-          pk[t] = pack_bf16x2(o0, o1);
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) {
+            // two hidden units at a time, packed fp32x2 math; the gate rows of W1 are halved when they are packed:
+            // silu(gate) * value = (h * tanh(h) + h) * value with h = gate / 2
+            const float h0 = __uint_as_float(xg[2 * t]), h1 = __uint_as_float(xg[2 * t + 1]);
+            const uint64_t h2 = pack_f32x2(h0, h1);
+            const uint64_t hid2 = mul_f32x2(fma_f32x2(h2, pack_f32x2(tanh_approx(h0), tanh_approx(h1)), h2),
+                                            pack_f32x2(__uint_as_float(xv[2 * t]), __uint_as_float(xv[2 * t + 1])));
+            float o0, o1;
+            unpack_f32x2(hid2, o0, o1);
+            pk[t] = pack_bf16x2(o0, o1);
+          }
         }
         // the H buffer's previous use (two chunks back) must have been consumed by its GEMM2
         ok = mbar_wait(bars + (H_FREE + e) * 8, (n & 1) ^ 1, abort_flag);
         if (!ok) break;
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          sts128(base + kSmH + e * 16384 + sw128_offset(m, c),
-                 make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]));
-        fence_proxy_async_smem();
+        tc_fence_after();
+        tmem_st32(lane_taddr + kTmemH + e * 32, pk);  // A operand of GEMM2
+        tmem_st_wait();
+        tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + (H_FULL + e) * 8);
       }
       if (!ok) break;
       // The next tile's statistics now, while the tensor core finishes this tile's last GEMM2 (its rows are in the
       // other X buffer already): the tile switch then only costs the output below.
-      float next_rstd = 1.f, next_nmr = 0.f;
       if (i + 1 < my_tiles) {
         ok = mbar_wait(bars + (X_FULL + (xs ^ 1)) * 8, ((i + 1) >> 1) & 1, abort_flag);
         if (!ok) break;
-        if (normalize) row_statistics(base + kSmX + (xs ^ 1) * 32768, m, p.eps, next_rstd, next_nmr);
+        // GEMM1 has read this tile's rows for the last time once its last chunk is complete
+        ok = mbar_wait(bars + XH_FREE * 8, i & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        normalise_row_to_tmem(base + kSmX + (xs ^ 1) * 32768, m, e, normalize, p.eps,
+                              reinterpret_cast<const float*>(gen + kSmLn), lane_taddr + kTmemX + e * 32);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + XH_FULL * 8);
       }
       // ---- output: columns [64e, 64e+64) of acc2 (+ residual) (* mask)
-      const int ab = i & 1;
-      ok = mbar_wait(bars + (ACC2_FULL + ab) * 8, (i >> 1) & 1, abort_flag);
+      ok = mbar_wait(bars + ACC2_FULL * 8, i & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
+      uint32_t acc[64];
+      tmem_ld32(lane_taddr + kTmemAcc2 + e * 64, reinterpret_cast<uint32_t(&)[32]>(acc[0]));
+      tmem_ld32(lane_taddr + kTmemAcc2 + e * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(acc[32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + ACC2_FREE * 8);  // the next tile's GEMM2 may start
       float mk = 1.f;
       if (p.mask != nullptr && row < p.rows) mk = __bfloat162float(p.mask[row]);
 #pragma unroll
       for (int g = 0; g < 2; ++g) {
-        uint32_t a[32];
-        tmem_ld32(lane_taddr + kTmemAcc2 + ab * 128 + e * 64 + g * 32, a);
-        tmem_ld_wait();
+        const uint32_t* a = acc + g * 32;
         uint32_t res[16];
         if (p.add_residual) {
 #pragma unroll
@@ -416,13 +459,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           tma_store_commit();
         }
       }
-      tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bars + (ACC2_FREE + ab) * 8);
-        mbar_arrive(bars + (X_EMPTY + xs) * 8);
-      }
-      rstd = next_rstd, nmr = next_nmr;
+      if (lane == 0) mbar_arrive(bars + (X_EMPTY + xs) * 8);
     }
     if (lane == 0) tma_store_wait_all();
   }
@@ -494,6 +532,7 @@ int launch_transition(const void* x, int64_t xs, const void* mask, const void* p
   p.sc = reinterpret_cast<const float2*>(pk + kTransScOff);
   p.flags = reinterpret_cast<const int*>(pk + kTransFlagsOff);
   p.b2 = reinterpret_cast<const float*>(pk + kTransB2Off);
+  p.ln = reinterpret_cast<const float*>(pk + kTransLnOff);
   p.mask = static_cast<const __nv_bfloat16*>(mask);
   p.eps = eps;
   p.add_residual = add_residual ? 1 : 0;
