@@ -25,7 +25,7 @@
 namespace b200ta {
 namespace {
 
-constexpr int kThreads = 384;
+constexpr int kThreads = 512;
 constexpr int kTileM = 128;
 constexpr int kChunk = 64;                 // hidden units per chunk
 constexpr int kChunks = kHidden / kChunk;  // 8
@@ -59,8 +59,8 @@ struct OutMaps {
 constexpr int kSmX = 0;                        // 2 x 32 KiB
 constexpr int kSmW1 = kSmX + 2 * 32768;        // 2 x 32 KiB: [k-half][64 value rows | 64 gate rows][64 ch]
 constexpr int kSmW2 = kSmW1 + 2 * 32768;       // 2 x 16 KiB: [128 out rows][64 hidden]
-constexpr int kSmH = kSmW2 + 2 * 16384;        // 2 x 16 KiB: [128 rows][64 hidden]
-constexpr int kSmOut = kSmH + 2 * 16384;       // 8 warps x 2 KiB staging slabs
+constexpr int kSmXn = kSmW2 + 2 * 16384;       // 2 x 16 KiB: the next tile's normalised rows, [channel half][128 rows][64 ch]
+constexpr int kSmOut = kSmXn + 2 * 16384;      // 8 warps x 2 KiB staging slabs
 constexpr int kSmSc = kSmOut + 8 * 2048;       // per pair of hidden units {rowsum0, rowsum1, const0, const1}: 256 value pairs, 256 gate pairs
 constexpr int kSmLn = kSmSc + 2 * 4096;        // gamma[128] | beta[128] as floats
 constexpr int kSmBars = kSmLn + 1024;
@@ -81,51 +81,83 @@ enum Bar {
 // work.
 constexpr uint32_t kTmemAcc1 = 0, kTmemAcc2 = 256, kTmemX = 384, kTmemH = 448, kTmemCols = 512;
 
-// Reads row m of an x tile in shared memory ([2 channel halves][128 rows][64 ch], 128-byte swizzle), takes its
-// LayerNorm statistics and stores channel half `e` of the normalised row, rounded to bf16 as the eager module's
-// LayerNorm output is, to tensor memory as the A operand of GEMM1.  `ln` holds {gamma[128], beta[128]} as floats;
-// normalize == false stores the raw row.
-__device__ __forceinline__ void normalise_row_to_tmem(uint32_t x0, int m, int e, bool normalize, float eps,
-                                                      const float* ln, uint32_t taddr) {
-  uint32_t v[64];
-#pragma unroll
-  for (int c = 0; c < 16; ++c) {
-    uint4 x = lds128(x0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
-    v[c * 4 + 0] = x.x, v[c * 4 + 1] = x.y, v[c * 4 + 2] = x.z, v[c * 4 + 3] = x.w;
-  }
-  uint32_t h[32];  // this warpgroup's 64 channels
-#pragma unroll
-  for (int j = 0; j < 32; ++j) h[j] = e ? v[32 + j] : v[j];
+// Row m of an x tile in shared memory ([2 channel halves][128 rows][64 ch], 128-byte swizzle) -> the same row,
+// layer-normalised and rounded to bf16 as the eager module's LayerNorm output is, in the staging tile (same
+// layout).  Three streaming passes over the row (sum, centred squares, normalise) in packed fp32x2 math with four
+// independent accumulators, so that the thread needs few registers.  `ln` = {gamma[128], beta[128]} in shared
+// memory; normalize == false copies the raw row.
+__device__ __forceinline__ void prepare_row(uint32_t x0, int m, bool normalize, float eps, const float* ln,
+                                            uint32_t stage0) {
+  float rstd = 1.f, nmr = 0.f;
   if (normalize) {
-    float sum = 0.f;
-#pragma unroll
-    for (int j = 0; j < 64; ++j) sum += bf16_lo(v[j]) + bf16_hi(v[j]);
-    const float mu = sum * (1.f / kC);
-    float var = 0.f;
-#pragma unroll
-    for (int j = 0; j < 64; ++j) {
-      const float d0 = bf16_lo(v[j]) - mu, d1 = bf16_hi(v[j]) - mu;
-      var = fmaf(d0, d0, var);
-      var = fmaf(d1, d1, var);
+    uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll 4
+    for (int c = 0; c < 16; ++c) {
+      const uint4 x = lds128(x0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
+      acc[0] = add_f32x2(acc[0], pack_f32x2(bf16_lo(x.x), bf16_hi(x.x)));
+      acc[1] = add_f32x2(acc[1], pack_f32x2(bf16_lo(x.y), bf16_hi(x.y)));
+      acc[2] = add_f32x2(acc[2], pack_f32x2(bf16_lo(x.z), bf16_hi(x.z)));
+      acc[3] = add_f32x2(acc[3], pack_f32x2(bf16_lo(x.w), bf16_hi(x.w)));
     }
-    const float rstd = rsqrtf(var * (1.f / kC) + eps);
-    const float nmr = -mu * rstd;
-    const uint64_t rstd2 = pack_f32x2(rstd, rstd), nmr2 = pack_f32x2(nmr, nmr);
-    const float2* gamma = reinterpret_cast<const float2*>(ln) + e * 32;
-    const float2* beta = reinterpret_cast<const float2*>(ln + kC) + e * 32;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      // gamma * (x - mu) * rstd + beta = x * (rstd * gamma) + (beta - mu * rstd * gamma)
-      const float2 g = gamma[j], bt = beta[j];
-      const uint64_t g2 = pack_f32x2(g.x, g.y);
-      const uint64_t y2 = fma_f32x2(pack_f32x2(bf16_lo(h[j]), bf16_hi(h[j])), mul_f32x2(rstd2, g2),
-                                    fma_f32x2(nmr2, g2, pack_f32x2(bt.x, bt.y)));
-      float y0, y1;
-      unpack_f32x2(y2, y0, y1);
-      h[j] = pack_bf16x2(y0, y1);
+    float a0, a1;
+    unpack_f32x2(add_f32x2(add_f32x2(acc[0], acc[1]), add_f32x2(acc[2], acc[3])), a0, a1);
+    const float mu = (a0 + a1) * (1.f / kC);
+    const uint64_t nmu2 = pack_f32x2(-mu, -mu);
+    acc[0] = acc[1] = acc[2] = acc[3] = 0ull;
+#pragma unroll 4
+    for (int c = 0; c < 16; ++c) {
+      const uint4 x = lds128(x0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
+      const uint64_t d0 = add_f32x2(pack_f32x2(bf16_lo(x.x), bf16_hi(x.x)), nmu2);
+      const uint64_t d1 = add_f32x2(pack_f32x2(bf16_lo(x.y), bf16_hi(x.y)), nmu2);
+      const uint64_t d2 = add_f32x2(pack_f32x2(bf16_lo(x.z), bf16_hi(x.z)), nmu2);
+      const uint64_t d3 = add_f32x2(pack_f32x2(bf16_lo(x.w), bf16_hi(x.w)), nmu2);
+      acc[0] = fma_f32x2(d0, d0, acc[0]);
+      acc[1] = fma_f32x2(d1, d1, acc[1]);
+      acc[2] = fma_f32x2(d2, d2, acc[2]);
+      acc[3] = fma_f32x2(d3, d3, acc[3]);
     }
+    unpack_f32x2(add_f32x2(add_f32x2(acc[0], acc[1]), add_f32x2(acc[2], acc[3])), a0, a1);
+    rstd = rsqrtf((a0 + a1) * (1.f / kC) + eps);
+    nmr = -mu * rstd;
   }
-  tmem_st32(taddr, h);
+  const uint64_t rstd2 = pack_f32x2(rstd, rstd), nmr2 = pack_f32x2(nmr, nmr);
+#pragma unroll 2
+  for (int c = 0; c < 16; ++c) {
+    const uint32_t off = (c >> 3) * 16384 + sw128_offset(m, c & 7);
+    uint4 x = lds128(x0 + off);
+    if (normalize) {
+      // gamma * (x - mu) * rstd + beta = x * (rstd * gamma) + (beta - mu * rstd * gamma); 8 channels per step
+      const float4 g0 = reinterpret_cast<const float4*>(ln)[2 * c], g1 = reinterpret_cast<const float4*>(ln)[2 * c + 1];
+      const float4 b0 = reinterpret_cast<const float4*>(ln + kC)[2 * c], b1 = reinterpret_cast<const float4*>(ln + kC)[2 * c + 1];
+      auto norm2 = [&](uint32_t w, float ga, float gb, float ba, float bb) -> uint32_t {
+        const uint64_t g2 = pack_f32x2(ga, gb);
+        const uint64_t y2 = fma_f32x2(pack_f32x2(bf16_lo(w), bf16_hi(w)), mul_f32x2(rstd2, g2),
+                                      fma_f32x2(nmr2, g2, pack_f32x2(ba, bb)));
+        float y0, y1;
+        unpack_f32x2(y2, y0, y1);
+        return pack_bf16x2(y0, y1);
+      };
+      x.x = norm2(x.x, g0.x, g0.y, b0.x, b0.y);
+      x.y = norm2(x.y, g0.z, g0.w, b0.z, b0.w);
+      x.z = norm2(x.z, g1.x, g1.y, b1.x, b1.y);
+      x.w = norm2(x.w, g1.z, g1.w, b1.z, b1.w);
+    }
+    sts128(stage0 + off, x);
+  }
+}
+
+// This thread's staged row (both channel halves) -> its lane of the A operand of GEMM1 in tensor memory.
+__device__ __forceinline__ void staged_row_to_tmem(uint32_t stage0, int m, uint32_t taddr) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t h[32];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 x = lds128(stage0 + half * 16384 + sw128_offset(m, c));
+      h[c * 4 + 0] = x.x, h[c * 4 + 1] = x.y, h[c * 4 + 2] = x.z, h[c * 4 + 3] = x.w;
+    }
+    tmem_st32(taddr + half * 32, h);
+  }
   tmem_st_wait();
 }
 
@@ -149,7 +181,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     abort_flag[1] = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + (X_FULL + i) * 8, 1);
-      mbar_init(bars + (X_EMPTY + i) * 8, 8);  // the 8 epilogue warps (residual)
+      mbar_init(bars + (X_EMPTY + i) * 8, 12);  // the 8 epilogue warps (residual) + the 4 row-preparation warps
       mbar_init(bars + (W1_FULL + i) * 8, 1);
       mbar_init(bars + (W1_EMPTY + i) * 8, 1);
       mbar_init(bars + (W2_FULL + i) * 8, 1);
@@ -161,7 +193,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
     mbar_init(bars + ACC2_FULL * 8, 1);
     mbar_init(bars + ACC2_FREE * 8, 8);
-    mbar_init(bars + XH_FULL * 8, 8);
+    mbar_init(bars + XH_FULL * 8, 4);
     mbar_init(bars + XH_FREE * 8, 1);
     fence_mbar_init();
   }
@@ -179,10 +211,38 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 
   const int my_tiles = (p.num_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1;
 
-  // Register budget: 168 per thread at launch; the helper warpgroup hands registers to the two SwiGLU warpgroups,
-  // which hold a whole accumulator row (128 values) at a time: 128 x 56 + 256 x 224 = 384 x 168.
+  // Register budget: 128 per thread at launch; the two helper warpgroups hand registers to the two SwiGLU
+  // warpgroups, which hold a whole accumulator row (128 values) at a time: 256 x 56 + 256 x 200 = 512 x 128.
   if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-  if (warp == 8) {
+  if (warp >= 12) {
+    // ------------------------------------------------------------------ row preparation warpgroup
+    // Thread = row: LayerNorm of the tile's rows into a staging tile as soon as the rows have arrived (a tile
+    // ahead of the GEMMs), then, once GEMM1 has finished with the previous tile, a copy into tensor memory as the
+    // A operand of GEMM1.  Only the copy sits on the tile switch's critical path.
+    const int m = (warp & 3) * 32 + lane;
+    const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
+    const bool normalize = __ldg(p.flags) != 0;
+    const float* ln_s = reinterpret_cast<const float*>(gen + kSmLn);
+    bool ok = true;
+    for (int i = 0; ok && i < my_tiles; ++i) {
+      const int xs = i & 1;
+      ok = mbar_wait(bars + (X_FULL + xs) * 8, (i >> 1) & 1, abort_flag);
+      if (!ok) break;
+      prepare_row(base + kSmX + xs * 32768, m, normalize, p.eps, ln_s, base + kSmXn);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + (X_EMPTY + xs) * 8);
+      if (i > 0) {  // GEMM1 has read the previous tile's rows for the last time once its last chunk is complete
+        ok = mbar_wait(bars + XH_FREE * 8, (i - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      staged_row_to_tmem(base + kSmXn, m, lane_taddr + kTmemX);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + XH_FULL * 8);
+    }
+  } else
+ if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer of x tiles and W1 chunks
     // (what GEMM1 needs; W2 has its own producer so that a W2 slot that frees late never holds back a W1 load)
     if (lane == 0) {
@@ -213,8 +273,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             tma_load_2d(dst, &tm_w1, f1, kh * 64, j * kChunk);                  // value rows
             tma_load_2d(dst + 8192, &tm_w1, f1, kh * 64, kHidden + j * kChunk);  // gate rows
           }
-          // the next tile's rows, early enough for its statistics to be taken before this tile ends
-          if (j == 3 && i + 1 < my_tiles) {
+          // the next tile's rows, early enough for the SwiGLU warpgroups to normalise them during this tile
+          if (j == 2 && i + 1 < my_tiles) {
             ok = load_x(i + 1);
             if (!ok) break;
           }
@@ -308,29 +368,18 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ SwiGLU / output warpgroups
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     const int e = warp >> 2;               // chunk parity and output column half this warpgroup owns
     const int m = (warp & 3) * 32 + lane;  // row inside the tile == TMEM lane
     const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     const uint32_t slab = base + kSmOut + warp * 2048;
     bool ok = true;
     int n = 0;  // uses of this warpgroup's acc1 / H buffers
-    const bool normalize = __ldg(p.flags) != 0;
     for (int i = 0; ok && i < my_tiles; ++i) {
       const int tile = blockIdx.x + i * gridDim.x;
       const int xs = i & 1;
       const long long row = (long long)tile * kTileM + m;
       const uint32_t x0 = base + kSmX + xs * 32768;
-      if (i == 0) {
-        ok = mbar_wait(bars + (X_FULL + xs) * 8, 0, abort_flag);
-        if (!ok) break;
-        // this warpgroup's channel half of the normalised row -> A operand of GEMM1
-        normalise_row_to_tmem(x0, m, e, normalize, p.eps, reinterpret_cast<const float*>(gen + kSmLn),
-                              lane_taddr + kTmemX + e * 32);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars + XH_FULL * 8);
-      }
       for (int j = e; ok && j < kChunks; j += 2, ++n) {
         ok = mbar_wait(bars + (ACC1_FULL + e) * 8, n & 1, abort_flag);
         if (!ok) break;
@@ -349,54 +398,44 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + (ACC1_FREE + e) * 8);
-        uint32_t pk[32];
-        if (kRelu) {
-          const float2* b1s = reinterpret_cast<const float2*>(gen + kSmSc) + j * (kChunk / 2);
-#pragma unroll
-          for (int t = 0; t < 32; ++t) {
-            const float2 b = b1s[t];
-            pk[t] = pack_bf16x2(fmaxf(__uint_as_float(xv[2 * t]) + b.x, 0.f), fmaxf(__uint_as_float(xv[2 * t + 1]) + b.y, 0.f));
-          }
-        } else {
-#pragma unroll
-          for (int t = 0; t < 32; ++t) {
-            // two hidden units at a time, packed fp32x2 math; the gate rows of W1 are halved when they are packed:
-            // silu(gate) * value = (h * tanh(h) + h) * value with h = gate / 2
-            const float h0 = __uint_as_float(xg[2 * t]), h1 = __uint_as_float(xg[2 * t + 1]);
-            const uint64_t h2 = pack_f32x2(h0, h1);
-            const uint64_t hid2 = mul_f32x2(fma_f32x2(h2, pack_f32x2(tanh_approx(h0), tanh_approx(h1)), h2),
-                                            pack_f32x2(__uint_as_float(xv[2 * t]), __uint_as_float(xv[2 * t + 1])));
-            float o0, o1;
-            unpack_f32x2(hid2, o0, o1);
-            pk[t] = pack_bf16x2(o0, o1);
-          }
-        }
-        // the H buffer's previous use (two chunks back) must have been consumed by its GEMM2
+        // the H buffer's previous use (two chunks back) must have been consumed by its GEMM2 (long done as a rule)
         ok = mbar_wait(bars + (H_FREE + e) * 8, (n & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        tmem_st32(lane_taddr + kTmemH + e * 32, pk);  // A operand of GEMM2
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {  // 32 hidden units at a time -> 16 columns of the A operand of GEMM2
+          uint32_t pk[16];
+          if (kRelu) {
+            const float2* b1s = reinterpret_cast<const float2*>(gen + kSmSc) + j * (kChunk / 2) + half * 16;
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+              const float2 b = b1s[t];
+              const int u = half * 32 + 2 * t;
+              pk[t] = pack_bf16x2(fmaxf(__uint_as_float(xv[u]) + b.x, 0.f), fmaxf(__uint_as_float(xv[u + 1]) + b.y, 0.f));
+            }
+          } else {
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+              // two hidden units at a time, packed fp32x2 math; the gate rows of W1 are halved when they are
+              // packed: silu(gate) * value = (h * tanh(h) + h) * value with h = gate / 2
+              const int u = half * 32 + 2 * t;
+              const float h0 = __uint_as_float(xg[u]), h1 = __uint_as_float(xg[u + 1]);
+              const uint64_t h2 = pack_f32x2(h0, h1);
+              const uint64_t hid2 = mul_f32x2(fma_f32x2(h2, pack_f32x2(tanh_approx(h0), tanh_approx(h1)), h2),
+                                              pack_f32x2(__uint_as_float(xv[u]), __uint_as_float(xv[u + 1])));
+              float o0, o1;
+              unpack_f32x2(hid2, o0, o1);
+              pk[t] = pack_bf16x2(o0, o1);
+            }
+          }
+          tmem_st16(lane_taddr + kTmemH + e * 32 + half * 16, pk);
+        }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + (H_FULL + e) * 8);
       }
       if (!ok) break;
-      // The next tile's statistics now, while the tensor core finishes this tile's last GEMM2 (its rows are in the
-      // other X buffer already): the tile switch then only costs the output below.
-      if (i + 1 < my_tiles) {
-        ok = mbar_wait(bars + (X_FULL + (xs ^ 1)) * 8, ((i + 1) >> 1) & 1, abort_flag);
-        if (!ok) break;
-        // GEMM1 has read this tile's rows for the last time once its last chunk is complete
-        ok = mbar_wait(bars + XH_FREE * 8, i & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        normalise_row_to_tmem(base + kSmX + (xs ^ 1) * 32768, m, e, normalize, p.eps,
-                              reinterpret_cast<const float*>(gen + kSmLn), lane_taddr + kTmemX + e * 32);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars + XH_FULL * 8);
-      }
       // ---- output: columns [64e, 64e+64) of acc2 (+ residual) (* mask)
       ok = mbar_wait(bars + ACC2_FULL * 8, i & 1, abort_flag);
       if (!ok) break;
@@ -408,6 +447,10 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + ACC2_FREE * 8);  // the next tile's GEMM2 may start
+      if (p.add_residual) {  // (long complete: the wait only orders this thread's reads after the TMA writes)
+        ok = mbar_wait(bars + (X_FULL + xs) * 8, (i >> 1) & 1, abort_flag);
+        if (!ok) break;
+      }
       float mk = 1.f;
       if (p.mask != nullptr && row < p.rows) mk = __bfloat162float(p.mask[row]);
 #pragma unroll
