@@ -70,7 +70,7 @@ constexpr int kSmDynamic = kSmTotal + 1024;
 enum Bar {
   X_FULL = 0, X_EMPTY = 2, W1_FULL = 4, W1_EMPTY = 6, W2_FULL = 8, W2_EMPTY = 10,
   ACC1_FULL = 12, ACC1_FREE = 14, H_FULL = 16, H_FREE = 18, ACC2_FULL = 20, ACC2_FREE = 21, XH_FULL = 22, XH_FREE = 23,
-  NUM_BARS = 24
+  XN_FULL = 24, XN_EMPTY = 25, NUM_BARS = 26
 };
 
 // Tensor memory: two GEMM1 accumulators (64 value + 64 gate columns each), the tile's output accumulator, the
@@ -83,45 +83,39 @@ constexpr uint32_t kTmemAcc1 = 0, kTmemAcc2 = 256, kTmemX = 384, kTmemH = 448, k
 
 // Row m of an x tile in shared memory ([2 channel halves][128 rows][64 ch], 128-byte swizzle) -> the same row,
 // layer-normalised and rounded to bf16 as the eager module's LayerNorm output is, in the staging tile (same
-// layout).  Three streaming passes over the row (sum, centred squares, normalise) in packed fp32x2 math with four
-// independent accumulators, so that the thread needs few registers.  `ln` = {gamma[128], beta[128]} in shared
+// layout).  Two streaming passes over the row (shifted sums, normalise) in packed fp32x2 math with four
+// independent accumulators each, so that the thread needs few registers.  `ln` = {gamma[128], beta[128]} in shared
 // memory; normalize == false copies the raw row.
 __device__ __forceinline__ void prepare_row(uint32_t x0, int m, bool normalize, float eps, const float* ln,
                                             uint32_t stage0) {
   float rstd = 1.f, nmr = 0.f;
   if (normalize) {
-    uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll 4
+    // One pass: sums of (x - k) and (x - k)^2 with k = the row's first channel (a shift keeps the variance
+    // formula E[d^2] - E[d]^2 free of cancellation when the row has a large common offset).
+    const float k = bf16_lo(lds128(x0 + sw128_offset(m, 0)).x);
+    const uint64_t nk2 = pack_f32x2(-k, -k);
+    uint64_t sa[4] = {0ull, 0ull, 0ull, 0ull}, sq[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll 8
     for (int c = 0; c < 16; ++c) {
       const uint4 x = lds128(x0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
-      acc[0] = add_f32x2(acc[0], pack_f32x2(bf16_lo(x.x), bf16_hi(x.x)));
-      acc[1] = add_f32x2(acc[1], pack_f32x2(bf16_lo(x.y), bf16_hi(x.y)));
-      acc[2] = add_f32x2(acc[2], pack_f32x2(bf16_lo(x.z), bf16_hi(x.z)));
-      acc[3] = add_f32x2(acc[3], pack_f32x2(bf16_lo(x.w), bf16_hi(x.w)));
+      const uint64_t d0 = add_f32x2(pack_f32x2(bf16_lo(x.x), bf16_hi(x.x)), nk2);
+      const uint64_t d1 = add_f32x2(pack_f32x2(bf16_lo(x.y), bf16_hi(x.y)), nk2);
+      const uint64_t d2 = add_f32x2(pack_f32x2(bf16_lo(x.z), bf16_hi(x.z)), nk2);
+      const uint64_t d3 = add_f32x2(pack_f32x2(bf16_lo(x.w), bf16_hi(x.w)), nk2);
+      sa[0] = add_f32x2(sa[0], d0), sa[1] = add_f32x2(sa[1], d1), sa[2] = add_f32x2(sa[2], d2), sa[3] = add_f32x2(sa[3], d3);
+      sq[0] = fma_f32x2(d0, d0, sq[0]), sq[1] = fma_f32x2(d1, d1, sq[1]);
+      sq[2] = fma_f32x2(d2, d2, sq[2]), sq[3] = fma_f32x2(d3, d3, sq[3]);
     }
-    float a0, a1;
-    unpack_f32x2(add_f32x2(add_f32x2(acc[0], acc[1]), add_f32x2(acc[2], acc[3])), a0, a1);
-    const float mu = (a0 + a1) * (1.f / kC);
-    const uint64_t nmu2 = pack_f32x2(-mu, -mu);
-    acc[0] = acc[1] = acc[2] = acc[3] = 0ull;
-#pragma unroll 4
-    for (int c = 0; c < 16; ++c) {
-      const uint4 x = lds128(x0 + (c >> 3) * 16384 + sw128_offset(m, c & 7));
-      const uint64_t d0 = add_f32x2(pack_f32x2(bf16_lo(x.x), bf16_hi(x.x)), nmu2);
-      const uint64_t d1 = add_f32x2(pack_f32x2(bf16_lo(x.y), bf16_hi(x.y)), nmu2);
-      const uint64_t d2 = add_f32x2(pack_f32x2(bf16_lo(x.z), bf16_hi(x.z)), nmu2);
-      const uint64_t d3 = add_f32x2(pack_f32x2(bf16_lo(x.w), bf16_hi(x.w)), nmu2);
-      acc[0] = fma_f32x2(d0, d0, acc[0]);
-      acc[1] = fma_f32x2(d1, d1, acc[1]);
-      acc[2] = fma_f32x2(d2, d2, acc[2]);
-      acc[3] = fma_f32x2(d3, d3, acc[3]);
-    }
-    unpack_f32x2(add_f32x2(add_f32x2(acc[0], acc[1]), add_f32x2(acc[2], acc[3])), a0, a1);
-    rstd = rsqrtf((a0 + a1) * (1.f / kC) + eps);
-    nmr = -mu * rstd;
+    float a0, a1, q0, q1;
+    unpack_f32x2(add_f32x2(add_f32x2(sa[0], sa[1]), add_f32x2(sa[2], sa[3])), a0, a1);
+    unpack_f32x2(add_f32x2(add_f32x2(sq[0], sq[1]), add_f32x2(sq[2], sq[3])), q0, q1);
+    const float md = (a0 + a1) * (1.f / kC);  // mean of x - k
+    const float var = fmaxf((q0 + q1) * (1.f / kC) - md * md, 0.f);
+    rstd = rsqrtf(var + eps);
+    nmr = -(md + k) * rstd;
   }
   const uint64_t rstd2 = pack_f32x2(rstd, rstd), nmr2 = pack_f32x2(nmr, nmr);
-#pragma unroll 2
+#pragma unroll 4
   for (int c = 0; c < 16; ++c) {
     const uint32_t off = (c >> 3) * 16384 + sw128_offset(m, c & 7);
     uint4 x = lds128(x0 + off);
@@ -181,7 +175,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     abort_flag[1] = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + (X_FULL + i) * 8, 1);
-      mbar_init(bars + (X_EMPTY + i) * 8, 12);  // the 8 epilogue warps (residual) + the 4 row-preparation warps
+      mbar_init(bars + (X_EMPTY + i) * 8, 8);  // the 8 epilogue warps (residual)
       mbar_init(bars + (W1_FULL + i) * 8, 1);
       mbar_init(bars + (W1_EMPTY + i) * 8, 1);
       mbar_init(bars + (W2_FULL + i) * 8, 1);
@@ -195,6 +189,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     mbar_init(bars + ACC2_FREE * 8, 8);
     mbar_init(bars + XH_FULL * 8, 4);
     mbar_init(bars + XH_FREE * 8, 1);
+    mbar_init(bars + XN_FULL * 8, 1);
+    mbar_init(bars + XN_EMPTY * 8, 4);
     fence_mbar_init();
   }
   // stage the constants: LayerNorm gamma | beta, and for the ReLU form the two linears' biases
@@ -212,35 +208,59 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int my_tiles = (p.num_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1;
 
   // Register budget: 128 per thread at launch; the two helper warpgroups hand registers to the two SwiGLU
-  // warpgroups, which hold a whole accumulator row (128 values) at a time: 256 x 56 + 256 x 200 = 512 x 128.
-  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  // warpgroups, which hold a whole accumulator row (128 values) at a time: 128 x 56 + 128 x 72 + 256 x 192 = 512 x 128.
+  if (warp >= 12) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  } else if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  }
   if (warp >= 12) {
     // ------------------------------------------------------------------ row preparation warpgroup
-    // Thread = row: LayerNorm of the tile's rows into a staging tile as soon as the rows have arrived (a tile
-    // ahead of the GEMMs), then, once GEMM1 has finished with the previous tile, a copy into tensor memory as the
-    // A operand of GEMM1.  Only the copy sits on the tile switch's critical path.
+    // Thread = row.  The warpgroup loads the tile's rows a second time, by its own TMA request into the staging
+    // tile, as soon as that tile is free (right after the previous copy, i.e. when the GEMMs of the tile before
+    // start) — the x ring's slots, which only feed the residual now, free too late for that.  It layer-normalises the
+    // rows in place and, once GEMM1 has finished with the previous tile, copies them into tensor memory as the A
+    // operand of GEMM1.  Only the copy sits on the tile switch's critical path.
     const int m = (warp & 3) * 32 + lane;
     const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     const bool normalize = __ldg(p.flags) != 0;
     const float* ln_s = reinterpret_cast<const float*>(gen + kSmLn);
+    const uint32_t xn = base + kSmXn;
+    auto request_rows = [&](int i) {  // one thread; the staging tile is free
+      const int tile = blockIdx.x + i * gridDim.x;
+      mbar_expect_tx(bars + XN_FULL * 8, 32768);
+      tma_load_2d(xn, &tm_x, bars + XN_FULL * 8, 0, tile * kTileM);
+      tma_load_2d(xn + 16384, &tm_x, bars + XN_FULL * 8, 64, tile * kTileM);
+    };
+    int requested = 0;
+    if (warp == 12 && lane == 0) request_rows(0), ++requested;
     bool ok = true;
     for (int i = 0; ok && i < my_tiles; ++i) {
-      const int xs = i & 1;
-      ok = mbar_wait(bars + (X_FULL + xs) * 8, (i >> 1) & 1, abort_flag);
+      ok = mbar_wait(bars + XN_FULL * 8, i & 1, abort_flag);
       if (!ok) break;
-      prepare_row(base + kSmX + xs * 32768, m, normalize, p.eps, ln_s, base + kSmXn);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bars + (X_EMPTY + xs) * 8);
+      prepare_row(xn, m, normalize, p.eps, ln_s, xn);
       if (i > 0) {  // GEMM1 has read the previous tile's rows for the last time once its last chunk is complete
         ok = mbar_wait(bars + XH_FREE * 8, (i - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
       }
-      staged_row_to_tmem(base + kSmXn, m, lane_taddr + kTmemX);
+      staged_row_to_tmem(xn, m, lane_taddr + kTmemX);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + XH_FULL * 8);
+      // once all 128 rows have been copied the staging tile can take the next tile's rows
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + XN_EMPTY * 8);
+      if (warp == 12 && lane == 0 && i + 1 < my_tiles) {
+        ok = mbar_wait(bars + XN_EMPTY * 8, i & 1, abort_flag);
+        if (ok) request_rows(i + 1), ++requested;
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
     }
+    // (on an abandoned wait a request may still be in flight: give it a bounded chance to land)
+    if (*abort_flag && warp == 12 && lane == 0 && requested > 0)
+      mbar_wait(bars + XN_FULL * 8, (requested - 1) & 1, abort_flag + 1);
   } else
  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer of x tiles and W1 chunks
@@ -368,7 +388,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ SwiGLU / output warpgroups
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
     const int e = warp >> 2;               // chunk parity and output column half this warpgroup owns
     const int m = (warp & 3) * 32 + lane;  // row inside the tile == TMEM lane
     const uint32_t lane_taddr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
