@@ -5,20 +5,18 @@
 //
 // A persistent CTA per SM walks 128-row tiles of x.  The hidden dimension is cut in
 // 8 chunks of 64 units; for each chunk
-//   GEMM1  acc1[128 x (64 value | 64 gate)] = x_tile · W1chunkᵀ   (tcgen05, K = 128, raw bf16 rows of x;
-//          LayerNorm is folded into W1 and finished in the epilogue with the row's mean / rstd)
-//   SwiGLU one thread per row: TMEM -> registers, value/gate affine, silu via tanh, product -> bf16
-//          tile H in shared memory (K-major, 128-byte swizzle = A operand of the next GEMM)
+//   GEMM1  acc1[128 x (64 value | 64 gate)] = x̂_tile · W1chunkᵀ   (tcgen05, K = 128; x̂ = the tile's rows after the
+//          LayerNorm, rounded to bf16 as the eager module's LayerNorm output is, A operand in tensor memory)
+//   SwiGLU one thread per row: TMEM -> registers, silu via tanh (gate rows of W1 are packed halved), product -> bf16
+//          tile H in tensor memory (A operand of the next GEMM)
 //   GEMM2  acc2[128 x 128] += H · W2chunkᵀ                        (tcgen05, K = 64)
 // W1/W2 chunks stream from L2 through two TMA rings; GEMM1 of chunk j+1 is issued before
 // GEMM2 of chunk j so the tensor core runs while the SwiGLU warps work.
 //
-// Warp roles (384 threads): warps 0-3 / 4-7 SwiGLU + output warpgroups (even / odd chunks),
-// warp 8 TMA producer of x and W1, warp 11 TMA producer of W2, warp 9 GEMM1 issuer / TMEM owner, warp 10 GEMM2 issuer.  The two GEMMs have
-// an issuing warp each because one thread issues a tcgen05.mma only about every 80-110 clocks: the 12 MMAs of a
-// chunk issued from one thread took 1100 of the 1500 clocks a chunk cost.  A SwiGLU warpgroup computes the next
-// tile's LayerNorm statistics before it waits for the current tile's last GEMM2, so the tile switch costs the
-// tensor core little.
+// Warp roles (512 threads): warps 0-3 / 4-7 SwiGLU + output warpgroups (even / odd chunks), warp 8 TMA producer of
+// x (residual copy) and W1, warp 11 TMA producer of W2, warp 9 GEMM1 issuer / TMEM owner, warp 10 GEMM2 issuer (both
+// warp-collective), warps 12-15 row preparation: they load the next tile's rows a second time into a staging tile,
+// layer-normalise them in place while the current tile's GEMMs run and copy them to tensor memory at the tile switch.
 #include "common.cuh"
 #include "layout.h"
 

@@ -5,8 +5,8 @@ Drop-in counterpart of ``Transition`` (``bionemo_ir/_torch/layers/transition.py:
 (``norm.{weight,bias}``, ``fused_fc2_fc1.weight`` with value rows first and gate rows second, ``fc3.weight``).
 The reference picks between three paths per call; here every call of the pair transition (dim 128, hidden 512) is
 the one fused kernel (``b200ta_transition``), which already does what the reference's ``transition_mlp_w_norm``
-path does: LayerNorm folded into the first linear, hidden activation kept on chip, mask and residual in the
-epilogue.  Other widths (the single-track transition, dim 384 and hidden 1536) run as row statistics plus two
+path does: LayerNorm applied on chip (the normalised rows, rounded to bf16 as the eager LayerNorm's output is, feed
+the first GEMM from tensor memory), hidden activation kept on chip, mask and residual in the epilogue.  Other widths (the single-track transition, dim 384 and hidden 1536) run as row statistics plus two
 tensor-core GEMMs (``b200ta_linear``): LayerNorm folded into the first, SwiGLU in its epilogue, the residual in
 the epilogue of the second.
 """

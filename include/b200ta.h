@@ -89,7 +89,8 @@ int b200ta_pack_node_weights(const void* ln_w, const void* ln_b, const void* w_i
 
 /*
  * ln_w, ln_b: [128].  w1: [1024,128] (fused_fc2_fc1: value rows first, gate rows
- * second).  w2: [128,512] (fc3).
+ * second).  w2: [128,512] (fc3).  The LayerNorm vectors are kept beside the bf16 weights (the kernel normalises
+ * the rows of x and rounds them to bf16 before the first GEMM, as the eager module does).
  */
 int b200ta_pack_transition_weights(const void* ln_w, const void* ln_b, const void* w1,
                                    const void* w2, int weight_dtype, void* packed, void* stream);
