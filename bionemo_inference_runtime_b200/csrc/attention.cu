@@ -140,9 +140,6 @@ __device__ __forceinline__ Item decode_item(const AttnParams& p, int item, int l
   it.nvalid = (it.q0 + kQTile < p.S) ? 2 : 1;
   return it;
 }
-__device__ __forceinline__ Item decode_item(const AttnParams& p, int item) {
-  return decode_item(p, item, item_raw_length(p, item));
-}
 
 // Walks the (item, key tile) sequence of one CTA in order, skipping items without work.
 struct TileCursor {

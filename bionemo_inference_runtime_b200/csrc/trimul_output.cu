@@ -262,7 +262,7 @@ trimul_output_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_cons
       const int tile = blockIdx.x + it * gridDim.x;
       const int jt = tile % p.tiles_j, bi = tile / p.tiles_j;
       const int i = bi % p.N, b = bi / p.N;
-      const int stage = it & 1, slot = it & 1;
+      const int slot = it & 1;
       const int j = jt * kTileM + m;
       // The residual values do not depend on the accumulators: fetch this thread's 2 x 32 channels (they were just
       // loaded as part of the z tile, so they come from L2) before waiting for the MMAs.
